@@ -1,0 +1,166 @@
+/*
+ * peer_b200 — C ABI of the B200 (sm_100a) PEER forward library.
+ *
+ * Every entry point takes plain device (or, where stated, pinned host)
+ * pointers and sizes; no C++ or framework types cross this boundary.  The
+ * caller owns every tensor, including the output; the library owns only the
+ * per-handle scratch it allocates in peer_create (normalised sub-keys,
+ * normalised queries, the selected (id, weight) tuples, a status word) and
+ * frees in peer_destroy.  All work is enqueued on the stream the caller
+ * passes; no entry point other than create/destroy/forward_host/query_status
+ * synchronises.
+ *
+ * Each declaration names the interface of wrmedford/llm720 that it replaces
+ * (paths relative to that project).
+ */
+#ifndef PEER_B200_H
+#define PEER_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PEER_B200_ABI_VERSION 1
+
+/* Return codes.  Nothing in this library falls back to another code path:
+ * an unsupported configuration is an error. */
+enum {
+    PEER_OK = 0,
+    PEER_ERR_INVALID_ARG = 1,   /* null pointer, bad size, misaligned pointer        */
+    PEER_ERR_UNSUPPORTED = 2,   /* configuration outside what the kernels implement  */
+    PEER_ERR_CUDA = 3,          /* a CUDA runtime call or launch failed              */
+    PEER_ERR_DEVICE_TIMEOUT = 4,/* a bounded device-side wait ran out                */
+    PEER_ERR_BOUNDS = 5         /* an expert id outside [0, num_experts) was seen    */
+};
+
+enum { PEER_DTYPE_F32 = 0, PEER_DTYPE_BF16 = 1, PEER_DTYPE_E4M3 = 2 };
+enum { PEER_ACT_GELU = 0, PEER_ACT_RELU = 1 };
+/* How the two per-dimension sub-key indices (i0, i1) become a flat expert id.
+ * REFERENCE: i0 + i1, what llm/models/experts.py:203-230 computes (the first
+ * dimension never receives its multiplier).  PRODUCT: i0 * n_keys1 + i1. */
+enum { PEER_INDEX_REFERENCE = 0, PEER_INDEX_PRODUCT = 1 };
+
+/* Mirrors the constructor of the reference module, PEER.__init__
+ * (llm/models/experts.py:46-61), and of the native operator
+ * PEEROperatorEnhanced (llm/models/kernels/peer_cutlass.h:13-23). */
+typedef struct peer_config {
+    int32_t abi_version;        /* PEER_B200_ABI_VERSION                              */
+    int32_t input_dim;
+    int32_t output_dim;
+    int64_t num_experts;        /* = n_keys0 * n_keys1                                */
+    int32_t top_k;              /* num_experts_per_tok, <= 32                         */
+    int32_t num_heads;
+    int32_t query_dim;          /* per head, even, <= 256                             */
+    int32_t n_keys0, n_keys1;   /* product_key_dim (two dimensions only)              */
+    int32_t expert_hidden_size; /* must be 1                                          */
+    int32_t activation;         /* PEER_ACT_*                                         */
+    int32_t norm_keys, norm_query, layer_norm; /* booleans (batch_norm_query = layer_norm) */
+    int32_t act_dtype;          /* dtype of x, out, query weights, LN affine, sub-keys: F32 or BF16 */
+    int32_t table_dtype;        /* dtype of expert_down / expert_up: F32, BF16 or E4M3 */
+    int32_t index_mode;         /* PEER_INDEX_*                                       */
+    int64_t max_tokens;         /* scratch capacity; longer inputs are processed in slices */
+} peer_config_t;
+
+/* Tensors of one forward call; all row-major and contiguous.
+ * Mirrors the argument list of the pybind entry `peer_forward`
+ * (llm/models/kernels/peer_cutlass_wrapper.cpp:65-88). */
+typedef struct peer_tensors {
+    const void*  x;            /* [T, input_dim]                 act_dtype            */
+    const void*  query_w;      /* [num_heads*query_dim, input_dim] act_dtype          */
+    const void*  query_b;      /* [num_heads*query_dim] or NULL  act_dtype            */
+    const void*  ln_w;         /* [query_dim] or NULL            act_dtype            */
+    const void*  ln_b;         /* [query_dim] or NULL            act_dtype            */
+    const void*  keys0;        /* [n_keys0, query_dim/2]         act_dtype            */
+    const void*  keys1;        /* [n_keys1, query_dim/2]         act_dtype            */
+    const void*  expert_down;  /* [num_experts, input_dim]       table_dtype          */
+    const void*  expert_up;    /* [num_experts, output_dim]      table_dtype          */
+    const float* down_scale;   /* [num_experts] (E4M3 tables) else NULL               */
+    const float* up_scale;     /* [num_experts] (E4M3 tables) else NULL               */
+    void*        out;          /* [T, output_dim]                act_dtype            */
+    int64_t*     ids_out;      /* optional [T, num_heads, top_k]: selected expert ids */
+    float*       scores_out;   /* optional [T, num_heads, top_k]: raw (pre-softmax) scores */
+} peer_tensors_t;
+
+typedef struct peer_op* peer_handle_t;
+
+/* Replaces the PEEROperatorEnhanced constructor + allocate_weights
+ * (llm/models/kernels/peer_cutlass.cu:1178-1305) and the process-global
+ * operator of peer_cutlass_wrapper.cpp:17-63.  One handle per module per
+ * device; not thread-safe.  Allocates the scratch on the current device. */
+int peer_create(const peer_config_t* cfg, peer_handle_t* out_handle);
+
+/* Replaces ~PEEROperatorEnhanced. */
+int peer_destroy(peer_handle_t h);
+
+/* Text of the last error on this handle (or of the last failed peer_create
+ * when h is NULL).  Replaces the exceptions thrown at
+ * peer_cutlass_wrapper.cpp:90-96 and peer_cutlass.cu:1388-1394. */
+const char* peer_last_error(peer_handle_t h);
+
+/* The whole layer on device buffers: replaces PEER.forward /
+ * PEER._forward_pytorch (llm/models/experts.py:288-384, 422-440) and
+ * PEEROperatorEnhanced::forward (peer_cutlass.cu:1307-1395).
+ * Asynchronous on `stream` (a cudaStream_t). */
+int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, void* stream);
+
+/* Same, with t->x and t->out (and the optional ids/scores outputs) in HOST
+ * memory (pinned for full speed): token slices are copied in, processed and
+ * copied out on three internal streams so transfers overlap the kernels.
+ * Returns after the last slice has landed in t->out.  Replaces the
+ * host-tensor call path of peer_forward_cutlass
+ * (llm/models/kernels/peer_cutlass.py:135-234). */
+int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens);
+
+/* Stage entry points (used by the parity tests and by callers that need one
+ * stage only). */
+
+/* Query projection + shared LayerNorm: experts.py:302-308.  Writes the
+ * queries after LayerNorm, fp32 [T, num_heads, query_dim]. */
+int peer_project_queries(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens,
+                         float* queries_out, void* stream);
+
+/* Product-key retrieval from given queries: PEER._get_expert_indices_pytorch
+ * (experts.py:138-285).  queries fp32 [T, num_heads, query_dim] (after
+ * LayerNorm, before the per-half L2 normalisation, exactly what the
+ * reference function receives).  Writes ids int64 and raw scores fp32,
+ * both [T, num_heads, top_k], sorted by descending score. */
+int peer_select(peer_handle_t h, const float* queries, const void* keys0, const void* keys1,
+                int64_t n_tokens, int64_t* ids_out, float* scores_out, void* stream);
+
+/* Expert evaluation from given selections: experts.py:327-382 with the
+ * softmax already applied.  ids int32 and weights fp32, both
+ * [T, num_heads*top_k]; out[t] = sum_j w[t,j] * act(down[ids[t,j]] . x[t]) * up[ids[t,j]]. */
+int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* ids, const float* weights,
+                     const void* expert_down, const void* expert_up, const float* down_scale,
+                     const float* up_scale, void* out, int64_t n_tokens, void* stream);
+
+/* Reads and clears the device status word (synchronises `stream`).  Returns
+ * PEER_OK, PEER_ERR_DEVICE_TIMEOUT or PEER_ERR_BOUNDS.  The kernels never
+ * trap: a bounded wait that runs out, or an expert id outside the table,
+ * is recorded there and the offending access is skipped. */
+int peer_query_status(peer_handle_t h, void* stream);
+
+/* Per-stage device timing, for benchmarks: while enabled, every slice of
+ * peer_forward / peer_forward_host records CUDA events on its stream around
+ * the three stage launches (query, select, expert evaluation).  Enabling or
+ * disabling discards pending measurements.  Replaces the cudaEvent timing of
+ * the reference's smoke_test (llm/models/kernels/peer_cutlass.cu:1468-1483). */
+int peer_stage_timing(peer_handle_t h, int enable);
+
+/* Waits for the recorded slices and returns the summed milliseconds of the
+ * three stages in ms3[0..2] and the number of slices in *n_slices; clears the
+ * record. */
+int peer_stage_times(peer_handle_t h, double* ms3, int64_t* n_slices);
+
+/* Number of kernel launches this handle has enqueued since creation. */
+int64_t peer_launch_count(peer_handle_t h);
+
+/* Library ABI version (PEER_B200_ABI_VERSION it was built with). */
+int peer_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PEER_B200_H */

@@ -1,0 +1,86 @@
+"""ctypes binding of ``libpeer_b200.so`` (the C ABI declared in
+``include/peer_b200.h``).  Nothing here computes anything: a missing library
+is an error, there is no other code path."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libpeer_b200.so")
+
+ABI_VERSION = 1
+OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_BOUNDS = range(6)
+DTYPE_F32, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2
+ACT_GELU, ACT_RELU = 0, 1
+INDEX_REFERENCE, INDEX_PRODUCT = 0, 1
+
+
+class PeerConfig(C.Structure):
+    _fields_ = [
+        ("abi_version", C.c_int32), ("input_dim", C.c_int32), ("output_dim", C.c_int32),
+        ("num_experts", C.c_int64), ("top_k", C.c_int32), ("num_heads", C.c_int32),
+        ("query_dim", C.c_int32), ("n_keys0", C.c_int32), ("n_keys1", C.c_int32),
+        ("expert_hidden_size", C.c_int32), ("activation", C.c_int32), ("norm_keys", C.c_int32),
+        ("norm_query", C.c_int32), ("layer_norm", C.c_int32), ("act_dtype", C.c_int32),
+        ("table_dtype", C.c_int32), ("index_mode", C.c_int32), ("max_tokens", C.c_int64),
+    ]
+
+
+class PeerTensors(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "x", "query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1", "expert_down", "expert_up",
+        "down_scale", "up_scale", "out", "ids_out", "scores_out")]
+
+
+EXPORTS = {
+    "peer_abi_version": (C.c_int, []),
+    "peer_create": (C.c_int, [C.POINTER(PeerConfig), C.POINTER(C.c_void_p)]),
+    "peer_destroy": (C.c_int, [C.c_void_p]),
+    "peer_last_error": (C.c_char_p, [C.c_void_p]),
+    "peer_forward": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p]),
+    "peer_forward_host": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64]),
+    "peer_project_queries": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p, C.c_void_p]),
+    "peer_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                              C.c_void_p, C.c_void_p]),
+    "peer_gather_eval": (C.c_int, [C.c_void_p] * 9 + [C.c_int64, C.c_void_p]),
+    "peer_query_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "peer_launch_count": (C.c_int64, [C.c_void_p]),
+    "peer_stage_timing": (C.c_int, [C.c_void_p, C.c_int]),
+    "peer_stage_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the library once.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m llm720_b200.build` "
+                "(needs nvcc; the library targets sm_100a).  There is no fallback path.")
+        lib = C.CDLL(LIB_PATH)
+        for name, (res, args) in EXPORTS.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        if lib.peer_abi_version() != ABI_VERSION:
+            raise RuntimeError("libpeer_b200.so was built from a different ABI version; rebuild it")
+        _lib = lib
+    return _lib
+
+
+def last_error(handle) -> str:
+    msg = load().peer_last_error(handle)
+    return msg.decode() if msg else ""
+
+
+def check(rc: int, handle=None) -> None:
+    """Raise the Python exception matching a non-zero return code."""
+    if rc == OK:
+        return
+    msg = last_error(handle)
+    if rc in (ERR_INVALID_ARG, ERR_UNSUPPORTED):
+        raise ValueError(f"peer_b200: {msg}")
+    raise RuntimeError(f"peer_b200 (code {rc}): {msg}")

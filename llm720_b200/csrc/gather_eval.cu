@@ -1,0 +1,321 @@
+// Expert evaluation: for every token, stream the selected experts' down rows
+// u_i and up rows v_i out of HBM, compute act(u_i . x) and accumulate
+// w_i * act(u_i . x) * v_i.  Nothing but the output row is written.
+//
+// Replaces llm/models/experts.py:332-382 (embedding lookups that materialise
+// two [T,H,k,D] tensors, two batched matmuls, the score weighting and both
+// reductions) with one pass over the selected rows.
+//
+// Organisation: one WARP owns one token.  The token's activation row and its
+// fp32 output accumulator live in that warp's registers for the whole token,
+// so no cross-warp reduction or CTA barrier is ever needed.  Each warp has a
+// private ring of row buffers in shared memory that lane 0 keeps full with
+// 1-D bulk copies (cp.async.bulk, completion on an mbarrier); u_0, v_0, u_1,
+// v_1 ... are issued STAGES rows ahead of their use, which is what keeps
+// enough bytes in flight (about 190 KB per SM) to cover HBM latency.
+// Every wait is bounded; a wait that runs out records STATUS_TIMEOUT and the
+// warp stops, it never spins forever.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace peer {
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int RING_BYTES_PER_WARP = 24 * 1024;
+constexpr int MAX_STAGES = 12;
+constexpr int MAX_SMEM = 227 * 1024;
+
+template <int CH> struct RingCfg {
+    static constexpr int SLOT = CH * 512;   // bytes: one row of up to CH 16-byte chunks per lane
+    static constexpr int ST0 = RING_BYTES_PER_WARP / SLOT;
+    static constexpr int STAGES = ST0 > MAX_STAGES ? MAX_STAGES : (ST0 < 2 ? 2 : ST0);
+};
+
+// ---- 16-byte chunk decoders: table storage -> fp32 -------------------------
+template <typename TT> struct Chunk;
+template <> struct Chunk<float> {
+    static constexpr int N = 4;
+    __device__ static __forceinline__ void decode(const uint4& c, float (&f)[N]) {
+        f[0] = __uint_as_float(c.x); f[1] = __uint_as_float(c.y);
+        f[2] = __uint_as_float(c.z); f[3] = __uint_as_float(c.w);
+    }
+};
+template <> struct Chunk<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static __forceinline__ void decode(const uint4& c, float (&f)[N]) {
+        f[0] = bf16_lo(c.x); f[1] = bf16_hi(c.x); f[2] = bf16_lo(c.y); f[3] = bf16_hi(c.y);
+        f[4] = bf16_lo(c.z); f[5] = bf16_hi(c.z); f[6] = bf16_lo(c.w); f[7] = bf16_hi(c.w);
+    }
+};
+template <> struct Chunk<__nv_fp8_e4m3> {
+    static constexpr int N = 16;
+    __device__ static __forceinline__ void pair(uint32_t two_bytes, float& a, float& b) {
+        const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(two_bytes), __NV_E4M3);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+        a = f.x; b = f.y;
+    }
+    __device__ static __forceinline__ void decode(const uint4& c, float (&f)[N]) {
+        pair(c.x & 0xffffu, f[0], f[1]);  pair(c.x >> 16, f[2], f[3]);
+        pair(c.y & 0xffffu, f[4], f[5]);  pair(c.y >> 16, f[6], f[7]);
+        pair(c.z & 0xffffu, f[8], f[9]);  pair(c.z >> 16, f[10], f[11]);
+        pair(c.w & 0xffffu, f[12], f[13]); pair(c.w >> 16, f[14], f[15]);
+    }
+};
+
+// ---- activation row: N consecutive elements of XT -> fp32 ------------------
+template <typename XT, int N> struct XIo;
+template <> struct XIo<float, 4> {
+    __device__ static __forceinline__ void load(const float* p, float* f) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p));
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    __device__ static __forceinline__ void store(float* p, const float* f) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    }
+};
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+template <> struct XIo<__nv_bfloat16, 8> {
+    __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+        const uint4 c = __ldg(reinterpret_cast<const uint4*>(p));
+        f[0] = bf16_lo(c.x); f[1] = bf16_hi(c.x); f[2] = bf16_lo(c.y); f[3] = bf16_hi(c.y);
+        f[4] = bf16_lo(c.z); f[5] = bf16_hi(c.z); f[6] = bf16_lo(c.w); f[7] = bf16_hi(c.w);
+    }
+    __device__ static __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+        *reinterpret_cast<uint4*>(p) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
+                                                  pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+    }
+};
+template <> struct XIo<__nv_bfloat16, 16> {
+    __device__ static __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+        XIo<__nv_bfloat16, 8>::load(p, f);
+        XIo<__nv_bfloat16, 8>::load(p + 8, f + 8);
+    }
+    __device__ static __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+        XIo<__nv_bfloat16, 8>::store(p, f);
+        XIo<__nv_bfloat16, 8>::store(p + 8, f + 8);
+    }
+};
+
+struct GatherParams {
+    const void* x; const int32_t* ids; const float* weights;
+    const char* down; const char* up; const float* down_scale; const float* up_scale;
+    void* out; int64_t T; int HK; int64_t N; int D, Dout; int activation; int* status;
+    int nch_u, nch_v;          // 16-byte chunks per down / up row
+};
+
+template <typename XT, typename TT, int CH>
+__global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherParams p) {
+    using RC = RingCfg<CH>;
+    constexpr int STAGES = RC::STAGES;
+    constexpr int SLOT = RC::SLOT;
+    constexpr int EPC = Chunk<TT>::N;            // elements per 16-byte chunk
+    constexpr bool SCALED = sizeof(TT) == 1;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // layout: [WARPS][STAGES][SLOT] ring | [WARPS][STAGES] mbarriers | per-warp entry lists
+    unsigned char* ring = smem + static_cast<size_t>(warp) * STAGES * SLOT;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(WARPS) * STAGES * SLOT) + warp * STAGES;
+    unsigned char* lists = smem + static_cast<size_t>(WARPS) * STAGES * SLOT + WARPS * STAGES * 8;
+    const int per_warp_list = p.HK * (SCALED ? 16 : 8);
+    int32_t* s_id = reinterpret_cast<int32_t*>(lists + static_cast<size_t>(warp) * per_warp_list);
+    float* s_w = reinterpret_cast<float*>(s_id + p.HK);
+    float* s_us = s_w + p.HK;       // only when SCALED
+    float* s_vs = s_us + p.HK;
+
+    const uint32_t ring_a = smem_u32(ring);
+    const uint32_t bars_a = smem_u32(bars);
+    if (lane == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(bars_a + 8 * s, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+
+    const uint32_t row_u = static_cast<uint32_t>(p.nch_u) * 16u, row_v = static_cast<uint32_t>(p.nch_v) * 16u;
+    const XT* __restrict__ xg = static_cast<const XT*>(p.x);
+    XT* __restrict__ og = static_cast<XT*>(p.out);
+    const int total_rows = 2 * p.HK;
+
+    int slot = 0;            // next ring slot to consume
+    uint32_t parity = 0;     // its phase
+    bool alive = true;
+
+    const int64_t nwarps = static_cast<int64_t>(gridDim.x) * WARPS;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * WARPS + warp; t < p.T && alive; t += nwarps) {
+        // ---- token prologue: selections into shared memory, x into registers
+        __syncwarp();
+        for (int e = lane; e < p.HK; e += 32) {
+            int32_t id = p.ids[t * p.HK + e];
+            float w = p.weights[t * p.HK + e];
+            if (static_cast<uint32_t>(id) >= static_cast<uint64_t>(p.N)) {
+                atomicMax(p.status, STATUS_BOUNDS);
+                id = 0; w = 0.f;
+            }
+            s_id[e] = id; s_w[e] = w;
+            if (SCALED) { s_us[e] = __ldg(p.down_scale + id); s_vs[e] = __ldg(p.up_scale + id); }
+        }
+        float xr[CH * EPC];
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const int c = lane + 32 * i;
+            if (c < p.nch_u) XIo<XT, EPC>::load(xg + t * p.D + c * EPC, xr + i * EPC);
+            else {
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) xr[i * EPC + e] = 0.f;
+            }
+        }
+        float acc[CH * EPC];
+#pragma unroll
+        for (int i = 0; i < CH * EPC; ++i) acc[i] = 0.f;
+        __syncwarp();
+
+        auto issue = [&](int r, int s) {      // lane 0 only: row r of this token into slot s
+            const int id = s_id[r >> 1];
+            const bool is_v = r & 1;
+            const char* src = is_v ? p.up + static_cast<int64_t>(id) * row_v
+                                   : p.down + static_cast<int64_t>(id) * row_u;
+            const uint32_t bytes = is_v ? row_v : row_u;
+            fence_proxy_async();
+            mbar_expect_tx(bars_a + 8 * s, bytes);
+            bulk_g2s(ring_a + s * SLOT, src, bytes, bars_a + 8 * s);
+        };
+        if (lane == 0) {
+            int s = slot;
+            for (int r = 0; r < STAGES && r < total_rows; ++r) {
+                issue(r, s);
+                if (++s == STAGES) s = 0;
+            }
+        }
+
+        for (int e = 0; e < p.HK; ++e) {
+            // ---- down row: dot with x
+            if (!mbar_wait(bars_a + 8 * slot, parity, p.status)) { alive = false; }
+            alive = __all_sync(FULL_MASK, alive);
+            if (!alive) break;
+            float d0 = 0.f, d1 = 0.f;
+            {
+                const unsigned char* rb = ring + slot * SLOT;
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < p.nch_u) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(rb + c * 16);
+                        float f[EPC];
+                        Chunk<TT>::decode(raw, f);
+#pragma unroll
+                        for (int q = 0; q < EPC; q += 2) {
+                            d0 = fmaf(f[q], xr[i * EPC + q], d0);
+                            d1 = fmaf(f[q + 1], xr[i * EPC + q + 1], d1);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && 2 * e + STAGES < total_rows) issue(2 * e + STAGES, slot);
+            if (++slot == STAGES) { slot = 0; parity ^= 1; }
+            float dot = warp_sum(d0 + d1);
+            if (SCALED) dot *= s_us[e];
+            float g = p.activation == PEER_ACT_GELU ? gelu_erf(dot) : fmaxf(dot, 0.f);
+            g *= s_w[e];
+            if (SCALED) g *= s_vs[e];
+
+            // ---- up row: accumulate
+            if (!mbar_wait(bars_a + 8 * slot, parity, p.status)) { alive = false; }
+            alive = __all_sync(FULL_MASK, alive);
+            if (!alive) break;
+            {
+                const unsigned char* rb = ring + slot * SLOT;
+#pragma unroll
+                for (int i = 0; i < CH; ++i) {
+                    const int c = lane + 32 * i;
+                    if (c < p.nch_v) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(rb + c * 16);
+                        float f[EPC];
+                        Chunk<TT>::decode(raw, f);
+#pragma unroll
+                        for (int q = 0; q < EPC; ++q) acc[i * EPC + q] = fmaf(g, f[q], acc[i * EPC + q]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0 && 2 * e + 1 + STAGES < total_rows) issue(2 * e + 1 + STAGES, slot);
+            if (++slot == STAGES) { slot = 0; parity ^= 1; }
+        }
+        if (!alive) break;
+
+#pragma unroll
+        for (int i = 0; i < CH; ++i) {
+            const int c = lane + 32 * i;
+            if (c < p.nch_v) XIo<XT, EPC>::store(og + t * p.Dout + c * EPC, acc + i * EPC);
+        }
+    }
+}
+
+template <typename XT, typename TT, int CH>
+size_t smem_bytes(int HK) {
+    using RC = RingCfg<CH>;
+    return static_cast<size_t>(WARPS) * RC::STAGES * RC::SLOT + WARPS * RC::STAGES * 8 +
+           static_cast<size_t>(WARPS) * HK * (sizeof(TT) == 1 ? 16 : 8);
+}
+
+template <typename XT, typename TT, int CH>
+cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
+    const size_t smem = smem_bytes<XT, TT, CH>(a.HK);
+    if (smem > MAX_SMEM) return cudaErrorInvalidValue;
+    static bool configured = false;     // per instantiation; the attribute is sticky per function
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    int64_t ctas = (a.T + WARPS - 1) / WARPS;
+    if (ctas > a.sm_count) ctas = a.sm_count;
+    gather_eval_kernel<XT, TT, CH><<<static_cast<unsigned>(ctas), THREADS, smem, s>>>(p);
+    return cudaGetLastError();
+}
+
+template <typename XT, typename TT>
+cudaError_t launch_ch(const GatherArgs& a, const GatherParams& p, int max_ch, cudaStream_t s) {
+    const int need = (max_ch + 31) / 32;     // chunks per lane
+    constexpr int EPL_LIMIT = 64;            // activation + accumulator registers per lane
+    constexpr int EPC = Chunk<TT>::N;
+    if (need * EPC > EPL_LIMIT && need > 1) return cudaErrorInvalidValue;
+    if (need <= 1) return launch_t<XT, TT, 1>(a, p, s);
+    if (need <= 2) return launch_t<XT, TT, 2>(a, p, s);
+    if (need <= 4) return launch_t<XT, TT, 4>(a, p, s);
+    if constexpr (EPC <= 8) { if (need <= 8) return launch_t<XT, TT, 8>(a, p, s); }
+    if constexpr (EPC <= 4) { if (need <= 16) return launch_t<XT, TT, 16>(a, p, s); }
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace
+
+cudaError_t gather_eval_setup() { return cudaSuccess; }
+
+cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
+    if (a.T == 0) return cudaSuccess;
+    const int tb = a.table_dtype == PEER_DTYPE_F32 ? 4 : (a.table_dtype == PEER_DTYPE_BF16 ? 2 : 1);
+    GatherParams p;
+    p.x = a.x; p.ids = a.ids; p.weights = a.weights;
+    p.down = static_cast<const char*>(a.down); p.up = static_cast<const char*>(a.up);
+    p.down_scale = a.down_scale; p.up_scale = a.up_scale; p.out = a.out; p.T = a.T; p.HK = a.HK;
+    p.N = a.N; p.D = a.D; p.Dout = a.Dout; p.activation = a.activation; p.status = a.status;
+    p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
+    const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
+    if (a.act_dtype == PEER_DTYPE_F32 && a.table_dtype == PEER_DTYPE_F32)
+        return launch_ch<float, float>(a, p, max_ch, s);
+    if (a.act_dtype == PEER_DTYPE_BF16 && a.table_dtype == PEER_DTYPE_BF16)
+        return launch_ch<__nv_bfloat16, __nv_bfloat16>(a, p, max_ch, s);
+    if (a.act_dtype == PEER_DTYPE_BF16 && a.table_dtype == PEER_DTYPE_E4M3)
+        return launch_ch<__nv_bfloat16, __nv_fp8_e4m3>(a, p, max_ch, s);
+    return cudaErrorInvalidValue;
+}
+
+}  // namespace peer

@@ -1,0 +1,76 @@
+// Internal launch interface between the C ABI (peer_api.cu) and the kernels.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace peer {
+
+// Largest number of (a, b) candidate pairs the combine step examines
+// (pairs with (a+1)(b+1) <= k for k <= 32 number at most 119).
+constexpr int MAX_PAIRS = 128;
+
+struct QueryArgs {
+    const void* x;        // [T, D] act dtype
+    const void* w;        // [H*Q, D] act dtype
+    const void* b;        // [H*Q] or null
+    const void* ln_w;     // [Q] or null (=1)
+    const void* ln_b;     // [Q] or null (=0)
+    float* q_ln_out;      // optional [T, H, Q]: queries after LayerNorm
+    float* q_hat_out;     // optional [T, H, Q]: halves L2-normalised
+    int64_t T;
+    int D, H, Q;
+    int layer_norm, norm_query;
+    int act_dtype;
+};
+cudaError_t launch_query_simt(const QueryArgs& a, cudaStream_t s);
+
+// rows of `width` elements -> fp32, each row divided by max(||row||, 1e-12) when do_norm;
+// written [rows, width], or [width, rows] when transpose_out
+cudaError_t launch_normalize_rows(const void* in, int in_dtype, int64_t rows, int width, int do_norm,
+                                  int transpose_out, float* out, cudaStream_t s);
+// [rows, Q] fp32 -> both halves of every row L2-normalised
+cudaError_t launch_normalize_halves(const float* q, int64_t rows, int Q, int do_norm, float* out,
+                                    cudaStream_t s);
+
+struct SelectArgs {
+    const float* q_hat;   // [rows, Q] fp32, halves normalised
+    const float* khat0;   // [Q/2, n0] fp32: normalised sub-keys, transposed
+    const float* khat1;   // [Q/2, n1] fp32
+    int64_t rows;         // T * H
+    int Q, n0, n1;
+    int kp0, kp1;         // candidates kept per half
+    int k;                // final top-k
+    int mult0, mult1;     // flat id = i0*mult0 + i1*mult1
+    const uint16_t* pairs;// device [n_pairs]: (a << 8) | b, candidate pairs of the combine step
+    int n_pairs;
+    int32_t* ids32;       // optional [rows, k]
+    float* weights;       // optional [rows, k] softmax over k
+    int64_t* ids64;       // optional [rows, k]
+    float* raw_scores;    // optional [rows, k]
+};
+cudaError_t launch_select_simt(const SelectArgs& a, cudaStream_t s);
+
+struct GatherArgs {
+    const void* x;            // [T, D] act dtype
+    const int32_t* ids;       // [T, HK]
+    const float* weights;     // [T, HK]
+    const void* down;         // [N, D] table dtype
+    const void* up;           // [N, Dout]
+    const float* down_scale;  // [N] or null
+    const float* up_scale;    // [N] or null
+    void* out;                // [T, Dout] act dtype
+    int64_t T;
+    int HK;
+    int64_t N;
+    int D, Dout;
+    int act_dtype, table_dtype, activation;
+    int* status;              // device status word
+    int sm_count;
+};
+cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s);
+// one-time per-process attribute set-up (dynamic shared memory opt-in)
+cudaError_t gather_eval_setup();
+cudaError_t select_simt_setup();
+
+}  // namespace peer

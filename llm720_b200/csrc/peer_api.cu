@@ -1,0 +1,492 @@
+// C ABI of the PEER forward library: handle management, argument checking
+// and the stage pipeline.  See include/peer_b200.h for the contract.
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "kernels.h"
+
+using namespace peer;
+
+struct peer_op {
+    peer_config_t cfg;
+    int device = 0;
+    int sm_count = 0;
+    int kp0 = 0, kp1 = 0, k_final = 0;
+    int mult0 = 1, mult1 = 1;
+    int n_pairs = 0;
+    // device scratch
+    float* khat0 = nullptr;       // [Q/2, n0] normalised sub-keys, transposed
+    float* khat1 = nullptr;       // [Q/2, n1]
+    float* q_hat = nullptr;       // [max_tokens, H, Q]
+    int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
+    float* sel_w = nullptr;       // [max_tokens, H*k]
+    uint16_t* pairs = nullptr;
+    int* status = nullptr;
+    // host-buffer pipeline (created on first peer_forward_host)
+    int64_t host_chunk = 0;
+    cudaStream_t st_in = nullptr, st_run = nullptr, st_out = nullptr;
+    cudaEvent_t ev_in[2] = {nullptr, nullptr}, ev_run[2] = {nullptr, nullptr}, ev_out[2] = {nullptr, nullptr};
+    void* d_x[2] = {nullptr, nullptr};
+    void* d_out[2] = {nullptr, nullptr};
+    int64_t* d_ids[2] = {nullptr, nullptr};
+    float* d_sc[2] = {nullptr, nullptr};
+    int64_t launches = 0;
+    // optional per-stage timing (peer_stage_timing): events recorded around each stage launch
+    bool timing = false;
+    std::vector<cudaEvent_t> tev;   // 4 per slice: before query, before select, before expert stage, after
+    size_t tev_used = 0;
+    std::string err;
+};
+
+static std::string g_create_error;
+
+static int fail(peer_op* h, int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (h) h->err = buf; else g_create_error = buf;
+    return code;
+}
+
+#define CU_TRY(h, expr)                                                                   \
+    do {                                                                                  \
+        cudaError_t e_ = (expr);                                                          \
+        if (e_ != cudaSuccess)                                                            \
+            return fail(h, PEER_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+    } while (0)
+
+static int act_bytes(int dt) { return dt == PEER_DTYPE_F32 ? 4 : (dt == PEER_DTYPE_BF16 ? 2 : 1); }
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// k' of the reference (llm/models/experts.py:168-187), two key dimensions.
+static int candidates_per_dim(int top_k, int dim_size) {
+    const int base = static_cast<int>(std::ceil(std::pow(static_cast<double>(top_k), 0.5))) + 2;
+    int kp = base < dim_size ? base : dim_size;
+    const int want = dim_size >= top_k ? top_k : dim_size;
+    if (kp < want) kp = want;
+    if (kp > dim_size) kp = dim_size;
+    return kp < 1 ? 1 : kp;
+}
+
+static void free_all(peer_op* h) {
+    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->sel_ids);
+    cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status);
+    for (int b = 0; b < 2; ++b) {
+        cudaFree(h->d_x[b]); cudaFree(h->d_out[b]); cudaFree(h->d_ids[b]); cudaFree(h->d_sc[b]);
+        if (h->ev_in[b]) cudaEventDestroy(h->ev_in[b]);
+        if (h->ev_run[b]) cudaEventDestroy(h->ev_run[b]);
+        if (h->ev_out[b]) cudaEventDestroy(h->ev_out[b]);
+    }
+    for (cudaEvent_t e : h->tev) cudaEventDestroy(e);
+    h->tev.clear();
+    if (h->st_in) cudaStreamDestroy(h->st_in);
+    if (h->st_run) cudaStreamDestroy(h->st_run);
+    if (h->st_out) cudaStreamDestroy(h->st_out);
+}
+
+extern "C" int peer_abi_version(void) { return PEER_B200_ABI_VERSION; }
+
+extern "C" const char* peer_last_error(peer_handle_t h) {
+    return h ? h->err.c_str() : g_create_error.c_str();
+}
+
+extern "C" int64_t peer_launch_count(peer_handle_t h) { return h ? h->launches : 0; }
+
+extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
+    if (!c || !out) return fail(nullptr, PEER_ERR_INVALID_ARG, "peer_create: null argument");
+    *out = nullptr;
+    if (c->abi_version != PEER_B200_ABI_VERSION)
+        return fail(nullptr, PEER_ERR_INVALID_ARG, "peer_create: abi_version %d, library has %d",
+                    c->abi_version, PEER_B200_ABI_VERSION);
+    if (c->expert_hidden_size != 1)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "expert_hidden_size=%d: only single-neuron experts (1) are implemented",
+                    c->expert_hidden_size);
+    if (c->activation != PEER_ACT_GELU && c->activation != PEER_ACT_RELU)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "activation %d is not implemented", c->activation);
+    if (c->act_dtype != PEER_DTYPE_F32 && c->act_dtype != PEER_DTYPE_BF16)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "act_dtype must be fp32 or bf16");
+    const bool combo = (c->act_dtype == PEER_DTYPE_F32 && c->table_dtype == PEER_DTYPE_F32) ||
+                       (c->act_dtype == PEER_DTYPE_BF16 && (c->table_dtype == PEER_DTYPE_BF16 || c->table_dtype == PEER_DTYPE_E4M3));
+    if (!combo)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "unsupported dtype pair: act %d, table %d (fp32/fp32, bf16/bf16, bf16/e4m3)",
+                    c->act_dtype, c->table_dtype);
+    if (c->input_dim <= 0 || c->output_dim <= 0 || c->num_heads <= 0 || c->top_k <= 0 || c->n_keys0 <= 0 ||
+        c->n_keys1 <= 0 || c->query_dim <= 0 || c->max_tokens <= 0)
+        return fail(nullptr, PEER_ERR_INVALID_ARG, "peer_create: non-positive dimension");
+    if (static_cast<int64_t>(c->n_keys0) * c->n_keys1 != c->num_experts)
+        return fail(nullptr, PEER_ERR_INVALID_ARG, "product of key dimensions %d x %d must equal num_experts %lld",
+                    c->n_keys0, c->n_keys1, static_cast<long long>(c->num_experts));
+    if (c->num_experts > 0x7fffffffLL)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "num_experts above 2^31-1");
+    if (c->query_dim % 2 || c->query_dim > 256)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "query_dim=%d: must be even and <= 256", c->query_dim);
+    if (c->input_dim % 8)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "input_dim=%d: must be a multiple of 8", c->input_dim);
+    const int tb = act_bytes(c->table_dtype);
+    if ((c->input_dim * tb) % 16 || (c->output_dim * tb) % 16 || (c->output_dim * act_bytes(c->act_dtype)) % 16)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "table rows and output rows must be multiples of 16 bytes");
+    if (c->top_k > 32)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "top_k=%d: at most 32", c->top_k);
+    if (c->index_mode != PEER_INDEX_REFERENCE && c->index_mode != PEER_INDEX_PRODUCT)
+        return fail(nullptr, PEER_ERR_INVALID_ARG, "index_mode %d", c->index_mode);
+
+    int dev = 0;
+    cudaDeviceProp prop;
+    CU_TRY(nullptr, cudaGetDevice(&dev));
+    CU_TRY(nullptr, cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                    dev, prop.major, prop.minor);
+
+    peer_op* h = new (std::nothrow) peer_op();
+    if (!h) return fail(nullptr, PEER_ERR_CUDA, "out of host memory");
+    h->cfg = *c;
+    h->device = dev;
+    h->sm_count = prop.multiProcessorCount;
+    h->kp0 = candidates_per_dim(c->top_k, c->n_keys0);
+    h->kp1 = candidates_per_dim(c->top_k, c->n_keys1);
+    if (h->kp0 > 32 || h->kp1 > 32) { delete h; return fail(nullptr, PEER_ERR_UNSUPPORTED, "more than 32 candidates per half"); }
+    const int64_t cand = static_cast<int64_t>(h->kp0) * h->kp1;
+    h->k_final = c->top_k < cand ? c->top_k : static_cast<int>(cand);
+    if (h->k_final != c->top_k) {
+        delete h;
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "top_k=%d exceeds the %lld candidates of a %dx%d key grid",
+                    c->top_k, static_cast<long long>(cand), c->n_keys0, c->n_keys1);
+    }
+    h->mult0 = c->index_mode == PEER_INDEX_PRODUCT ? c->n_keys1 : 1;
+    h->mult1 = 1;
+
+    std::vector<uint16_t> pairs;
+    for (int a = 0; a < h->kp0; ++a)
+        for (int b = 0; b < h->kp1; ++b)
+            if ((a + 1) * (b + 1) <= h->k_final) pairs.push_back(static_cast<uint16_t>((a << 8) | b));
+    h->n_pairs = static_cast<int>(pairs.size());
+    if (h->n_pairs > MAX_PAIRS) { delete h; return fail(nullptr, PEER_ERR_UNSUPPORTED, "too many candidate pairs"); }
+
+    const int hw = c->query_dim / 2;
+    const int64_t HK = static_cast<int64_t>(c->num_heads) * c->top_k;
+    cudaError_t e = cudaSuccess;
+    auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, bytes); };
+    alloc(reinterpret_cast<void**>(&h->khat0), sizeof(float) * hw * c->n_keys0);
+    alloc(reinterpret_cast<void**>(&h->khat1), sizeof(float) * hw * c->n_keys1);
+    alloc(reinterpret_cast<void**>(&h->q_hat), sizeof(float) * c->max_tokens * c->num_heads * c->query_dim);
+    alloc(reinterpret_cast<void**>(&h->sel_ids), sizeof(int32_t) * c->max_tokens * HK);
+    alloc(reinterpret_cast<void**>(&h->sel_w), sizeof(float) * c->max_tokens * HK);
+    alloc(reinterpret_cast<void**>(&h->pairs), sizeof(uint16_t) * MAX_PAIRS);
+    alloc(reinterpret_cast<void**>(&h->status), sizeof(int));
+    if (e == cudaSuccess) e = cudaMemcpy(h->pairs, pairs.data(), sizeof(uint16_t) * pairs.size(), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
+    if (e == cudaSuccess) e = select_simt_setup();
+    if (e == cudaSuccess) e = gather_eval_setup();
+    if (e != cudaSuccess) {
+        fail(nullptr, PEER_ERR_CUDA, "peer_create: %s", cudaGetErrorString(e));
+        free_all(h);
+        delete h;
+        return PEER_ERR_CUDA;
+    }
+    *out = h;
+    return PEER_OK;
+}
+
+extern "C" int peer_destroy(peer_handle_t h) {
+    if (!h) return PEER_OK;
+    cudaDeviceSynchronize();
+    free_all(h);
+    delete h;
+    return PEER_OK;
+}
+
+static int check_tensors(peer_op* h, const peer_tensors_t* t, bool need_tables) {
+    const peer_config_t& c = h->cfg;
+    if (!t) return fail(h, PEER_ERR_INVALID_ARG, "null tensor struct");
+    if (!t->x || !t->query_w || !t->keys0 || !t->keys1)
+        return fail(h, PEER_ERR_INVALID_ARG, "x, query_w, keys0 and keys1 are required");
+    if (need_tables) {
+        if (!t->expert_down || !t->expert_up || !t->out)
+            return fail(h, PEER_ERR_INVALID_ARG, "expert_down, expert_up and out are required");
+        if (c.table_dtype == PEER_DTYPE_E4M3 && (!t->down_scale || !t->up_scale))
+            return fail(h, PEER_ERR_INVALID_ARG, "FP8 tables need down_scale and up_scale");
+        if (!aligned16(t->expert_down) || !aligned16(t->expert_up) || !aligned16(t->out))
+            return fail(h, PEER_ERR_INVALID_ARG, "expert tables and out must be 16-byte aligned");
+    }
+    if (!aligned16(t->x) || !aligned16(t->query_w))
+        return fail(h, PEER_ERR_INVALID_ARG, "x and query_w must be 16-byte aligned");
+    return PEER_OK;
+}
+
+static int normalise_keys(peer_op* h, const void* keys0, const void* keys1, cudaStream_t s) {
+    const peer_config_t& c = h->cfg;
+    const int hw = c.query_dim / 2;
+    CU_TRY(h, launch_normalize_rows(keys0, c.act_dtype, c.n_keys0, hw, c.norm_keys, 1, h->khat0, s));
+    CU_TRY(h, launch_normalize_rows(keys1, c.act_dtype, c.n_keys1, hw, c.norm_keys, 1, h->khat1, s));
+    h->launches += 2;
+    return PEER_OK;
+}
+
+static SelectArgs select_args(peer_op* h, int64_t n_tokens) {
+    const peer_config_t& c = h->cfg;
+    SelectArgs a{};
+    a.q_hat = h->q_hat; a.khat0 = h->khat0; a.khat1 = h->khat1;
+    a.rows = n_tokens * c.num_heads; a.Q = c.query_dim; a.n0 = c.n_keys0; a.n1 = c.n_keys1;
+    a.kp0 = h->kp0; a.kp1 = h->kp1; a.k = h->k_final; a.mult0 = h->mult0; a.mult1 = h->mult1;
+    a.pairs = h->pairs; a.n_pairs = h->n_pairs;
+    return a;
+}
+
+// One slice (n <= max_tokens) of the layer, all pointers on the device.
+static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, void* out, int64_t* ids_out,
+                         float* scores_out, int64_t n, cudaStream_t s) {
+    const peer_config_t& c = h->cfg;
+    QueryArgs q{};
+    q.x = x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
+    q.q_ln_out = nullptr; q.q_hat_out = h->q_hat; q.T = n; q.D = c.input_dim; q.H = c.num_heads;
+    q.Q = c.query_dim; q.layer_norm = c.layer_norm; q.norm_query = c.norm_query; q.act_dtype = c.act_dtype;
+    cudaEvent_t* ev = nullptr;
+    if (h->timing) {
+        if (h->tev_used + 4 > h->tev.size()) {
+            for (int i = 0; i < 4; ++i) {
+                cudaEvent_t e;
+                CU_TRY(h, cudaEventCreate(&e));
+                h->tev.push_back(e);
+            }
+        }
+        ev = &h->tev[h->tev_used];
+        h->tev_used += 4;
+        CU_TRY(h, cudaEventRecord(ev[0], s));
+    }
+    CU_TRY(h, launch_query_simt(q, s));
+    if (ev) CU_TRY(h, cudaEventRecord(ev[1], s));
+
+    SelectArgs sa = select_args(h, n);
+    sa.ids32 = h->sel_ids; sa.weights = h->sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
+    CU_TRY(h, launch_select_simt(sa, s));
+    if (ev) CU_TRY(h, cudaEventRecord(ev[2], s));
+
+    GatherArgs g{};
+    g.x = x; g.ids = h->sel_ids; g.weights = h->sel_w; g.down = t->expert_down; g.up = t->expert_up;
+    g.down_scale = t->down_scale; g.up_scale = t->up_scale; g.out = out; g.T = n;
+    g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
+    g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
+    g.status = h->status; g.sm_count = h->sm_count;
+    cudaError_t e = launch_gather_eval(g, s);
+    if (e == cudaErrorInvalidValue)
+        return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
+                    c.input_dim, c.output_dim, g.HK);
+    CU_TRY(h, e);
+    if (ev) CU_TRY(h, cudaEventRecord(ev[3], s));
+    h->launches += 3;
+    return PEER_OK;
+}
+
+extern "C" int peer_stage_timing(peer_handle_t h, int enable) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    h->timing = enable != 0;
+    h->tev_used = 0;
+    return PEER_OK;
+}
+
+extern "C" int peer_stage_times(peer_handle_t h, double* ms3, int64_t* n_slices) {
+    if (!h || !ms3 || !n_slices) return PEER_ERR_INVALID_ARG;
+    ms3[0] = ms3[1] = ms3[2] = 0.0;
+    *n_slices = static_cast<int64_t>(h->tev_used / 4);
+    for (size_t i = 0; i + 4 <= h->tev_used; i += 4) {
+        CU_TRY(h, cudaEventSynchronize(h->tev[i + 3]));
+        for (int j = 0; j < 3; ++j) {
+            float ms = 0.f;
+            CU_TRY(h, cudaEventElapsedTime(&ms, h->tev[i + j], h->tev[i + j + 1]));
+            ms3[j] += ms;
+        }
+    }
+    h->tev_used = 0;
+    return PEER_OK;
+}
+
+extern "C" int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens < 0) return fail(h, PEER_ERR_INVALID_ARG, "negative token count");
+    if (n_tokens == 0) return PEER_OK;
+    int rc = check_tensors(h, t, true);
+    if (rc) return rc;
+    const peer_config_t& c = h->cfg;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rc = normalise_keys(h, t->keys0, t->keys1, s);
+    if (rc) return rc;
+    const int ab = act_bytes(c.act_dtype);
+    const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += c.max_tokens) {
+        const int64_t n = n_tokens - t0 < c.max_tokens ? n_tokens - t0 : c.max_tokens;
+        rc = forward_slice(h, t, static_cast<const char*>(t->x) + t0 * c.input_dim * ab,
+                           static_cast<char*>(t->out) + t0 * c.output_dim * ab,
+                           t->ids_out ? t->ids_out + t0 * HK : nullptr,
+                           t->scores_out ? t->scores_out + t0 * HK : nullptr, n, s);
+        if (rc) return rc;
+    }
+    return PEER_OK;
+}
+
+static int host_pipeline_setup(peer_op* h, bool want_ids) {
+    const peer_config_t& c = h->cfg;
+    if (!h->st_in) {
+        // two rounds of one-token-per-warp of the expert stage, capped by the scratch
+        int64_t chunk = static_cast<int64_t>(h->sm_count) * 8 * 2;
+        if (chunk > c.max_tokens) chunk = c.max_tokens;
+        h->host_chunk = chunk;
+        CU_TRY(h, cudaStreamCreateWithFlags(&h->st_in, cudaStreamNonBlocking));
+        CU_TRY(h, cudaStreamCreateWithFlags(&h->st_run, cudaStreamNonBlocking));
+        CU_TRY(h, cudaStreamCreateWithFlags(&h->st_out, cudaStreamNonBlocking));
+        const int ab = act_bytes(c.act_dtype);
+        for (int b = 0; b < 2; ++b) {
+            CU_TRY(h, cudaEventCreateWithFlags(&h->ev_in[b], cudaEventDisableTiming));
+            CU_TRY(h, cudaEventCreateWithFlags(&h->ev_run[b], cudaEventDisableTiming));
+            CU_TRY(h, cudaEventCreateWithFlags(&h->ev_out[b], cudaEventDisableTiming));
+            CU_TRY(h, cudaMalloc(&h->d_x[b], static_cast<size_t>(chunk) * c.input_dim * ab));
+            CU_TRY(h, cudaMalloc(&h->d_out[b], static_cast<size_t>(chunk) * c.output_dim * ab));
+        }
+    }
+    if (want_ids && !h->d_ids[0]) {
+        const size_t n = static_cast<size_t>(h->host_chunk) * c.num_heads * c.top_k;
+        for (int b = 0; b < 2; ++b) {
+            CU_TRY(h, cudaMalloc(reinterpret_cast<void**>(&h->d_ids[b]), n * sizeof(int64_t)));
+            CU_TRY(h, cudaMalloc(reinterpret_cast<void**>(&h->d_sc[b]), n * sizeof(float)));
+        }
+    }
+    return PEER_OK;
+}
+
+extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens < 0) return fail(h, PEER_ERR_INVALID_ARG, "negative token count");
+    if (n_tokens == 0) return PEER_OK;
+    if (!t || !t->x || !t->out) return fail(h, PEER_ERR_INVALID_ARG, "x and out are required");
+    const peer_config_t& c = h->cfg;
+    const bool want_ids = t->ids_out || t->scores_out;
+    int rc = host_pipeline_setup(h, want_ids);
+    if (rc) return rc;
+    peer_tensors_t dt = *t;
+    dt.x = h->d_x[0]; dt.out = h->d_out[0];
+    rc = check_tensors(h, &dt, true);
+    if (rc) return rc;
+    rc = normalise_keys(h, t->keys0, t->keys1, h->st_run);
+    if (rc) return rc;
+
+    const int ab = act_bytes(c.act_dtype);
+    const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
+    const int64_t chunk = h->host_chunk;
+    int64_t i = 0;
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += chunk, ++i) {
+        const int b = static_cast<int>(i & 1);
+        const int64_t n = n_tokens - t0 < chunk ? n_tokens - t0 : chunk;
+        // x staging buffer b is free once the kernels of slice i-2 are done
+        if (i >= 2) CU_TRY(h, cudaStreamWaitEvent(h->st_in, h->ev_run[b], 0));
+        CU_TRY(h, cudaMemcpyAsync(h->d_x[b], static_cast<const char*>(t->x) + t0 * c.input_dim * ab,
+                                  static_cast<size_t>(n) * c.input_dim * ab, cudaMemcpyHostToDevice, h->st_in));
+        CU_TRY(h, cudaEventRecord(h->ev_in[b], h->st_in));
+        CU_TRY(h, cudaStreamWaitEvent(h->st_run, h->ev_in[b], 0));
+        // out staging buffer b is free once slice i-2 has been copied out
+        if (i >= 2) CU_TRY(h, cudaStreamWaitEvent(h->st_run, h->ev_out[b], 0));
+        rc = forward_slice(h, t, h->d_x[b], h->d_out[b], want_ids ? h->d_ids[b] : nullptr,
+                           want_ids ? h->d_sc[b] : nullptr, n, h->st_run);
+        if (rc) return rc;
+        CU_TRY(h, cudaEventRecord(h->ev_run[b], h->st_run));
+        CU_TRY(h, cudaStreamWaitEvent(h->st_out, h->ev_run[b], 0));
+        CU_TRY(h, cudaMemcpyAsync(static_cast<char*>(t->out) + t0 * c.output_dim * ab, h->d_out[b],
+                                  static_cast<size_t>(n) * c.output_dim * ab, cudaMemcpyDeviceToHost, h->st_out));
+        if (t->ids_out)
+            CU_TRY(h, cudaMemcpyAsync(t->ids_out + t0 * HK, h->d_ids[b], static_cast<size_t>(n) * HK * sizeof(int64_t),
+                                      cudaMemcpyDeviceToHost, h->st_out));
+        if (t->scores_out)
+            CU_TRY(h, cudaMemcpyAsync(t->scores_out + t0 * HK, h->d_sc[b], static_cast<size_t>(n) * HK * sizeof(float),
+                                      cudaMemcpyDeviceToHost, h->st_out));
+        CU_TRY(h, cudaEventRecord(h->ev_out[b], h->st_out));
+    }
+    CU_TRY(h, cudaStreamSynchronize(h->st_out));
+    CU_TRY(h, cudaStreamSynchronize(h->st_run));
+    return PEER_OK;
+}
+
+extern "C" int peer_project_queries(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens,
+                                    float* queries_out, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    if (!queries_out) return fail(h, PEER_ERR_INVALID_ARG, "queries_out is null");
+    int rc = check_tensors(h, t, false);
+    if (rc) return rc;
+    const peer_config_t& c = h->cfg;
+    QueryArgs q{};
+    q.x = t->x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
+    q.q_ln_out = queries_out; q.q_hat_out = nullptr; q.T = n_tokens; q.D = c.input_dim; q.H = c.num_heads;
+    q.Q = c.query_dim; q.layer_norm = c.layer_norm; q.norm_query = c.norm_query; q.act_dtype = c.act_dtype;
+    CU_TRY(h, launch_query_simt(q, static_cast<cudaStream_t>(stream)));
+    h->launches += 1;
+    return PEER_OK;
+}
+
+extern "C" int peer_select(peer_handle_t h, const float* queries, const void* keys0, const void* keys1,
+                           int64_t n_tokens, int64_t* ids_out, float* scores_out, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    if (!queries || !keys0 || !keys1) return fail(h, PEER_ERR_INVALID_ARG, "queries and keys are required");
+    const peer_config_t& c = h->cfg;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int rc = normalise_keys(h, keys0, keys1, s);
+    if (rc) return rc;
+    const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
+    const int64_t HQ = static_cast<int64_t>(c.num_heads) * c.query_dim;
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += c.max_tokens) {
+        const int64_t n = n_tokens - t0 < c.max_tokens ? n_tokens - t0 : c.max_tokens;
+        CU_TRY(h, launch_normalize_halves(queries + t0 * HQ, n * c.num_heads, c.query_dim, c.norm_query, h->q_hat, s));
+        SelectArgs sa = select_args(h, n);
+        sa.ids64 = ids_out ? ids_out + t0 * HK : nullptr;
+        sa.raw_scores = scores_out ? scores_out + t0 * HK : nullptr;
+        CU_TRY(h, launch_select_simt(sa, s));
+        h->launches += 2;
+    }
+    return PEER_OK;
+}
+
+extern "C" int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* ids, const float* weights,
+                                const void* expert_down, const void* expert_up, const float* down_scale,
+                                const float* up_scale, void* out, int64_t n_tokens, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    const peer_config_t& c = h->cfg;
+    if (!x || !ids || !weights || !expert_down || !expert_up || !out)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval: null pointer");
+    if (c.table_dtype == PEER_DTYPE_E4M3 && (!down_scale || !up_scale))
+        return fail(h, PEER_ERR_INVALID_ARG, "FP8 tables need down_scale and up_scale");
+    if (!aligned16(x) || !aligned16(expert_down) || !aligned16(expert_up) || !aligned16(out))
+        return fail(h, PEER_ERR_INVALID_ARG, "x, tables and out must be 16-byte aligned");
+    GatherArgs g{};
+    g.x = x; g.ids = ids; g.weights = weights; g.down = expert_down; g.up = expert_up;
+    g.down_scale = down_scale; g.up_scale = up_scale; g.out = out; g.T = n_tokens;
+    g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
+    g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
+    g.status = h->status; g.sm_count = h->sm_count;
+    cudaError_t e = launch_gather_eval(g, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue)
+        return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
+                    c.input_dim, c.output_dim, g.HK);
+    CU_TRY(h, e);
+    h->launches += 1;
+    return PEER_OK;
+}
+
+extern "C" int peer_query_status(peer_handle_t h, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int st = 0;
+    CU_TRY(h, cudaMemcpyAsync(&st, h->status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    CU_TRY(h, cudaMemsetAsync(h->status, 0, sizeof(int), s));
+    CU_TRY(h, cudaStreamSynchronize(s));
+    if (st == STATUS_TIMEOUT) return fail(h, PEER_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out");
+    if (st == STATUS_BOUNDS) return fail(h, PEER_ERR_BOUNDS, "an expert id outside [0, num_experts) was skipped");
+    return PEER_OK;
+}

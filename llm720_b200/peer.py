@@ -1,0 +1,382 @@
+"""Drop-in ``PEER`` module and operator wrapper over the CUDA library.
+
+``PEER`` has the constructor, parameter names/shapes (so state-dicts load
+both ways), ``forward(hidden_states)`` signature and output shape of the
+reference module (llm/models/experts.py:37-440).  The forward pass runs
+entirely in the sm_100a kernels behind ``libpeer_b200.so``; there is no
+PyTorch or CPU implementation behind it, and anything the kernels do not
+implement raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+
+_DT = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16,
+       torch.float8_e4m3fn: _lib.DTYPE_E4M3}
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def _stream(device) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+class PeerOp:
+    """One native operator handle (``peer_create`` ... ``peer_destroy``).
+
+    Plays the role of ``PEEROperatorEnhanced`` in the reference
+    (llm/models/kernels/peer_cutlass.h:11-57): holds the configuration and the
+    device scratch, and launches the kernels on the caller's stream."""
+
+    def __init__(self, *, input_dim: int, output_dim: int, num_heads: int, query_dim: int,
+                 product_key_dim, top_k: int, act_dtype: torch.dtype, table_dtype: torch.dtype,
+                 activation: str = "gelu", norm_keys: bool = True, norm_query: bool = True,
+                 layer_norm: bool = True, index_mode: str = "reference", max_tokens: int = 16384,
+                 expert_hidden_size: int = 1, device=None):
+        if len(product_key_dim) != 2:
+            raise ValueError(f"product_key_dim={list(product_key_dim)}: only two key dimensions are implemented")
+        if activation not in ("gelu", "relu"):
+            raise ValueError(f"Unsupported activation: {activation}")
+        if index_mode not in ("reference", "product"):
+            raise ValueError(f"index_mode={index_mode!r}: 'reference' or 'product'")
+        if act_dtype not in (torch.float32, torch.bfloat16) or table_dtype not in _DT:
+            raise ValueError(f"unsupported dtypes: activations {act_dtype}, tables {table_dtype}")
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("peer_b200 runs on CUDA devices only (sm_100a); there is no CPU path")
+        self.lib = _lib.load()
+        cfg = _lib.PeerConfig(
+            abi_version=_lib.ABI_VERSION, input_dim=input_dim, output_dim=output_dim,
+            num_experts=int(product_key_dim[0]) * int(product_key_dim[1]), top_k=top_k,
+            num_heads=num_heads, query_dim=query_dim, n_keys0=int(product_key_dim[0]),
+            n_keys1=int(product_key_dim[1]), expert_hidden_size=expert_hidden_size,
+            activation=_lib.ACT_GELU if activation == "gelu" else _lib.ACT_RELU,
+            norm_keys=int(norm_keys), norm_query=int(norm_query), layer_norm=int(layer_norm),
+            act_dtype=_DT[act_dtype], table_dtype=_DT[table_dtype],
+            index_mode=_lib.INDEX_REFERENCE if index_mode == "reference" else _lib.INDEX_PRODUCT,
+            max_tokens=int(max_tokens))
+        self.cfg = cfg
+        self.act_dtype, self.table_dtype = act_dtype, table_dtype
+        self.handle = C.c_void_p()
+        with torch.cuda.device(self.device):
+            rc = self.lib.peer_create(C.byref(cfg), C.byref(self.handle))
+        if rc != _lib.OK:
+            self.handle = C.c_void_p()
+            _lib.check(rc, None)
+
+    # -- plumbing -----------------------------------------------------------
+    def close(self):
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            self.lib.peer_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc):
+        _lib.check(rc, self.handle)
+
+    def _dev(self, t: torch.Tensor, name: str, dtype=None, host_ok=False) -> torch.Tensor:
+        if t is None:
+            return None
+        if not host_ok and t.device != self.device:
+            raise RuntimeError(f"{name} is on {t.device}, the operator on {self.device}")
+        if dtype is not None and t.dtype != dtype:
+            raise TypeError(f"{name} has dtype {t.dtype}, expected {dtype}")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous")
+        return t
+
+    def _tensors(self, x, w: dict, out, ids_out=None, scores_out=None, host_io=False) -> _lib.PeerTensors:
+        a, tb = self.act_dtype, self.table_dtype
+        self._dev(x, "x", a, host_ok=host_io)
+        self._dev(out, "out", a, host_ok=host_io)
+        for k in ("query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1"):
+            self._dev(w.get(k), k, a)
+        for k in ("expert_down", "expert_up"):
+            self._dev(w.get(k), k, tb)
+        for k in ("down_scale", "up_scale"):
+            self._dev(w.get(k), k, torch.float32)
+        return _lib.PeerTensors(
+            x=x.data_ptr(), query_w=w["query_w"].data_ptr(),
+            query_b=None if w.get("query_b") is None else w["query_b"].data_ptr(),
+            ln_w=None if w.get("ln_w") is None else w["ln_w"].data_ptr(),
+            ln_b=None if w.get("ln_b") is None else w["ln_b"].data_ptr(),
+            keys0=w["keys0"].data_ptr(), keys1=w["keys1"].data_ptr(),
+            expert_down=None if w.get("expert_down") is None else w["expert_down"].data_ptr(),
+            expert_up=None if w.get("expert_up") is None else w["expert_up"].data_ptr(),
+            down_scale=None if w.get("down_scale") is None else w["down_scale"].data_ptr(),
+            up_scale=None if w.get("up_scale") is None else w["up_scale"].data_ptr(),
+            out=None if out is None else out.data_ptr(),
+            ids_out=None if ids_out is None else ids_out.data_ptr(),
+            scores_out=None if scores_out is None else scores_out.data_ptr())
+
+    # -- entry points -------------------------------------------------------
+    def forward(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None):
+        """x [T, D] -> out [T, D_out] on the device, asynchronously on the current stream."""
+        T = x.shape[0]
+        t = self._tensors(x, w, out, ids_out, scores_out)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_forward(self.handle, C.byref(t), T, _stream(self.device)))
+
+    def forward_host(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None):
+        """x and out in (pinned) host memory; returns when out is complete."""
+        if x.device.type != "cpu" or out.device.type != "cpu":
+            raise RuntimeError("forward_host takes host tensors for x and out")
+        t = self._tensors(x, w, out, ids_out, scores_out, host_io=True)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_forward_host(self.handle, C.byref(t), x.shape[0]))
+
+    def project_queries(self, x: torch.Tensor, w: dict) -> torch.Tensor:
+        T = x.shape[0]
+        q = torch.empty(T, self.cfg.num_heads, self.cfg.query_dim, dtype=torch.float32, device=self.device)
+        t = self._tensors(x, w, None)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_project_queries(self.handle, C.byref(t), T, _ptr(q), _stream(self.device)))
+        return q
+
+    def select(self, queries: torch.Tensor, keys0: torch.Tensor, keys1: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """queries fp32 [T, H, Q] (after LayerNorm) -> (ids int64, raw scores fp32) [T, H, k]."""
+        self._dev(queries, "queries", torch.float32)
+        self._dev(keys0, "keys0", self.act_dtype)
+        self._dev(keys1, "keys1", self.act_dtype)
+        T = queries.shape[0]
+        ids = torch.empty(T, self.cfg.num_heads, self.cfg.top_k, dtype=torch.int64, device=self.device)
+        sc = torch.empty(T, self.cfg.num_heads, self.cfg.top_k, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_select(self.handle, _ptr(queries), _ptr(keys0), _ptr(keys1), T,
+                                             _ptr(ids), _ptr(sc), _stream(self.device)))
+        return ids, sc
+
+    def gather_eval(self, x, ids32, weights, down, up, down_scale=None, up_scale=None, out=None):
+        """out[t] = sum_j weights[t,j] * act(down[ids[t,j]] . x[t]) * up[ids[t,j]]."""
+        self._dev(x, "x", self.act_dtype)
+        self._dev(ids32, "ids", torch.int32)
+        self._dev(weights, "weights", torch.float32)
+        self._dev(down, "expert_down", self.table_dtype)
+        self._dev(up, "expert_up", self.table_dtype)
+        self._dev(down_scale, "down_scale", torch.float32)
+        self._dev(up_scale, "up_scale", torch.float32)
+        T = x.shape[0]
+        if out is None:
+            out = torch.empty(T, self.cfg.output_dim, dtype=self.act_dtype, device=self.device)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_gather_eval(self.handle, _ptr(x), _ptr(ids32), _ptr(weights), _ptr(down),
+                                                  _ptr(up), _ptr(down_scale), _ptr(up_scale), _ptr(out), T,
+                                                  _stream(self.device)))
+        return out
+
+    def query_status(self):
+        """Synchronise and raise if a kernel recorded a timeout or an out-of-range id."""
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_query_status(self.handle, _stream(self.device)))
+
+    def stage_timing(self, enable: bool):
+        """Record CUDA events around the three stage launches of every following forward."""
+        self._check(self.lib.peer_stage_timing(self.handle, int(enable)))
+
+    def stage_times(self):
+        """(ms_query, ms_select, ms_experts, n_slices) summed since the last read; synchronises."""
+        ms = (C.c_double * 3)()
+        n = C.c_int64()
+        self._check(self.lib.peer_stage_times(self.handle, ms, C.byref(n)))
+        return ms[0], ms[1], ms[2], int(n.value)
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.peer_launch_count(self.handle))
+
+
+class PEER(nn.Module):
+    """Parameter Efficient Expert Retrieval layer on the B200 kernels.
+
+    Same constructor arguments and defaults as the reference
+    (llm/models/experts.py:46-61); same parameters: ``query_proj`` (Linear with
+    bias), ``query_layer_norm`` (LayerNorm(query_dim) shared by all heads, or
+    None), ``sub_keys`` (two ``[n_i, query_dim/2]`` tables), ``expert_down`` /
+    ``expert_up`` (Embedding tables).
+
+    Attributes that may be set after construction (keyword filtering in
+    ``TransformerBlock`` passes constructor names only, foundation.py:135-147):
+
+    * ``index_mode``: ``"reference"`` (flat id = i0 + i1, what the reference's
+      PyTorch forward computes) or ``"product"`` (i0 * n1 + i1).
+    * ``track_indices``: when true (default, as in the reference) every forward
+      stores ``_last_expert_indices`` (int64 [B,S,H,k]) and
+      ``_last_expert_scores`` (raw scores, fp32).
+    * ``max_slice_tokens``: token capacity of the scratch; longer inputs run in
+      slices.
+    """
+
+    def __init__(self, input_dim: int, output_dim: int, num_experts: int, num_experts_per_tok: int = 16,
+                 num_heads: int = 8, expert_hidden_size: int = 1, query_dim: int = 256,
+                 product_key_dim: List[int] = [32, 32], activation: str = "gelu", dropout: float = 0.0,
+                 norm_keys: bool = True, norm_query: bool = True, batch_norm_query: bool = True):
+        super().__init__()
+        self.input_dim = input_dim
+        self.output_dim = output_dim
+        self.num_experts = num_experts
+        self.num_experts_per_tok = num_experts_per_tok
+        self.num_heads = num_heads
+        self.expert_hidden_size = expert_hidden_size
+        self.query_dim = query_dim
+        self.product_key_dim = list(product_key_dim)
+        self.norm_keys = norm_keys
+        self.norm_query = norm_query
+        self.batch_norm_query = batch_norm_query
+        self.activation_name = activation
+
+        if math.prod(self.product_key_dim) != num_experts:
+            raise AssertionError(f"Product of dimensions {self.product_key_dim} = {math.prod(self.product_key_dim)} "
+                                 f"must equal the number of experts {num_experts}")
+        if activation not in ("relu", "gelu"):
+            raise ValueError(f"Unsupported activation: {activation}")
+        if len(self.product_key_dim) != 2:
+            raise ValueError("peer_b200 implements two-dimensional product keys only")
+        if expert_hidden_size != 1:
+            raise ValueError("peer_b200 implements single-neuron experts (expert_hidden_size=1) only")
+
+        self.query_proj = nn.Linear(input_dim, num_heads * query_dim)
+        self.query_layer_norm = nn.LayerNorm(query_dim) if batch_norm_query else None
+        self.sub_keys = nn.ParameterList()
+        sub = query_dim // len(self.product_key_dim)
+        for n in self.product_key_dim:
+            self.sub_keys.append(nn.Parameter(torch.empty(n, sub).normal_(0.0, 0.02)))
+        self.expert_down = nn.Embedding(num_experts, input_dim * expert_hidden_size)
+        self.expert_up = nn.Embedding(num_experts, output_dim * expert_hidden_size)
+        self.dropout = nn.Dropout(dropout)
+        self.register_buffer("expert_down_scale", None, persistent=True)
+        self.register_buffer("expert_up_scale", None, persistent=True)
+
+        self.index_mode = "reference"
+        self.track_indices = True
+        self.max_slice_tokens = 16384
+        self._last_expert_indices: Optional[torch.Tensor] = None
+        self._last_expert_scores: Optional[torch.Tensor] = None
+        self._op: Optional[PeerOp] = None
+        self._op_key = None
+
+    # -- FP8 tables ---------------------------------------------------------
+    @torch.no_grad()
+    def quantize_tables_e4m3(self):
+        """Replace both expert tables by FP8-e4m3 payloads with a per-row fp32
+        scale (absmax/448)."""
+        from .synthetic import quantize_rows_e4m3
+        for name in ("expert_down", "expert_up"):
+            emb = getattr(self, name)
+            q, s = quantize_rows_e4m3(emb.weight.data)
+            emb.weight = nn.Parameter(q, requires_grad=False)
+            setattr(self, name + "_scale", s)
+        return self
+
+    # -- operator management -------------------------------------------------
+    def _weights(self) -> dict:
+        ln = self.query_layer_norm
+        return dict(query_w=self.query_proj.weight, query_b=self.query_proj.bias,
+                    ln_w=None if ln is None else ln.weight, ln_b=None if ln is None else ln.bias,
+                    keys0=self.sub_keys[0], keys1=self.sub_keys[1], expert_down=self.expert_down.weight,
+                    expert_up=self.expert_up.weight, down_scale=self.expert_down_scale,
+                    up_scale=self.expert_up_scale)
+
+    def _operator(self, device, act_dtype, n_tokens: int) -> PeerOp:
+        cap = min(max(n_tokens, 1), self.max_slice_tokens)
+        table_dtype = self.expert_down.weight.dtype
+        key = (str(device), act_dtype, table_dtype, self.index_mode, self.activation_name,
+               self.norm_keys, self.norm_query, self.batch_norm_query)
+        if self._op is None or self._op_key != key or self._op.cfg.max_tokens < cap:
+            if self._op is not None:
+                cap = max(cap, self._op.cfg.max_tokens) if self._op_key == key else cap
+                self._op.close()
+            self._op = PeerOp(input_dim=self.input_dim, output_dim=self.output_dim, num_heads=self.num_heads,
+                              query_dim=self.query_dim, product_key_dim=self.product_key_dim,
+                              top_k=self.num_experts_per_tok, act_dtype=act_dtype, table_dtype=table_dtype,
+                              activation=self.activation_name, norm_keys=self.norm_keys,
+                              norm_query=self.norm_query, layer_norm=self.batch_norm_query,
+                              index_mode=self.index_mode, max_tokens=cap, device=device)
+            self._op_key = key
+        return self._op
+
+    def _prepare(self, hidden_states: torch.Tensor):
+        if hidden_states.dim() != 3 or hidden_states.shape[-1] != self.input_dim:
+            raise ValueError(f"hidden_states must be [batch, seq, {self.input_dim}], got {tuple(hidden_states.shape)}")
+        if self.training and self.dropout.p > 0:
+            raise RuntimeError("peer_b200 is a forward (inference) path: dropout in training mode is not implemented")
+        if torch.is_grad_enabled() and (hidden_states.requires_grad or any(p.requires_grad for p in self.parameters())):
+            raise RuntimeError("peer_b200 implements the forward pass only; call it under torch.no_grad() "
+                               "(or freeze the parameters)")
+        w = self._weights()
+        dt = self.query_proj.weight.dtype
+        if hidden_states.dtype != dt:
+            raise TypeError(f"hidden_states is {hidden_states.dtype} but the module's parameters are {dt}")
+        return w, dt
+
+    # -- forward --------------------------------------------------------------
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """[batch, seq, input_dim] -> [batch, seq, output_dim], same dtype (experts.py:422-440)."""
+        w, dt = self._prepare(hidden_states)
+        if hidden_states.device.type != "cuda":
+            raise RuntimeError("peer_b200 runs on CUDA devices only (sm_100a); there is no CPU path. "
+                               "Use forward_host() to feed pinned host buffers.")
+        B, S, _ = hidden_states.shape
+        T = B * S
+        x = hidden_states.contiguous().view(T, self.input_dim)
+        op = self._operator(x.device, dt, T)
+        out = torch.empty(T, self.output_dim, dtype=dt, device=x.device)
+        ids = sc = None
+        if self.track_indices:
+            ids = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.int64, device=x.device)
+            sc = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.float32, device=x.device)
+        op.forward(x, w, out, ids, sc)
+        self._stash(ids, sc, B, S)
+        return out.view(B, S, self.output_dim)
+
+    def forward_host(self, hidden_states: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Same layer for a HOST tensor (pinned for full speed): slices are copied to the device,
+        processed and copied back on overlapping streams.  Returns a host tensor."""
+        w, dt = self._prepare(hidden_states)
+        if hidden_states.device.type != "cpu":
+            raise RuntimeError("forward_host takes a host tensor")
+        B, S, _ = hidden_states.shape
+        T = B * S
+        x = hidden_states.contiguous().view(T, self.input_dim)
+        dev = self.query_proj.weight.device
+        op = self._operator(dev, dt, T)
+        if out is None:
+            out = torch.empty(B, S, self.output_dim, dtype=dt, pin_memory=True)
+        ids = sc = None
+        if self.track_indices:
+            ids = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.int64, pin_memory=True)
+            sc = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.float32, pin_memory=True)
+        op.forward_host(x, w, out.view(T, self.output_dim), ids, sc)
+        self._stash(ids, sc, B, S)
+        return out
+
+    def _stash(self, ids, sc, B, S):
+        if ids is not None:
+            self._last_expert_indices = ids.view(B, S, self.num_heads, self.num_experts_per_tok)
+            self._last_expert_scores = sc.view(B, S, self.num_heads, self.num_experts_per_tok)
+
+    @torch.no_grad()
+    def select(self, queries: torch.Tensor, top_k: Optional[int] = None):
+        """Counterpart of ``_get_expert_indices_pytorch`` (experts.py:138-285):
+        queries [B,S,H,Q] after LayerNorm -> (indices int64, raw scores) [B,S,H,k]."""
+        if top_k is not None and top_k != self.num_experts_per_tok:
+            raise ValueError("top_k must equal num_experts_per_tok")
+        B, S, H, Q = queries.shape
+        op = self._operator(queries.device, self.sub_keys[0].dtype, B * S)
+        ids, sc = op.select(queries.float().contiguous().view(B * S, H, Q), self.sub_keys[0], self.sub_keys[1])
+        return ids.view(B, S, H, -1), sc.view(B, S, H, -1).to(queries.dtype)
+
+    _get_expert_indices = select

@@ -1,0 +1,338 @@
+"""Parity of the CUDA path (called through the C ABI) with the oracle and
+with the golden files generated from the reference module.
+
+Tolerances (stated by the build target):
+  * selected ids: equal as ordered lists, except inside groups whose
+    reference scores differ by < 1e-6 relative (near ties);
+  * fp32 layers: output max-abs <= 2e-6 + 1e-5 * max|ref|, L1-relative <= 1e-5;
+  * bf16 layers: against bf16(fp32 oracle on the same bf16 values):
+    max-abs <= 2e-2 and L1-relative <= 1e-3;
+  * FP8 tables: same bf16 bound against the oracle run on the DEQUANTISED
+    tables; against the oracle run on the original bf16 tables the looser
+    bound max-abs <= 5e-2, L1-relative <= 8e-2 (e4m3 keeps 4 significant bits).
+"""
+import numpy as np
+import pytest
+import torch
+
+from llm720_b200 import PEER, PeerOp, peer_forward, synthetic as syn
+from oracle import peer_oracle as orc
+from _util import load_golden, make_op, op_weights, oracle_shape, oracle_weights
+
+pytestmark = pytest.mark.gpu
+
+
+def check_ids(ids, ref_ids, ref_sc, sc, min_exact=0.995):
+    n, exact, near, bad = orc.compare_selection(ids.cpu(), ref_ids, ref_sc, sc.cpu())
+    assert bad == 0, f"{bad} of {n} rows differ outside near-ties ({exact} exact, {near} near-tie)"
+    assert exact >= min_exact * n, (n, exact, near)
+
+
+def check_out(out, ref, dtype):
+    if dtype == torch.float32:
+        mx, l1 = orc.output_errors(out.cpu(), ref)
+        assert mx <= 2e-6 + 1e-5 * float(ref.abs().max()) and l1 <= 1e-5, (mx, l1)
+    else:
+        mx, l1 = orc.output_errors(out.cpu().float(), ref.to(dtype).float())
+        assert mx <= 2e-2 and l1 <= 1e-3, (mx, l1)
+    return mx, l1
+
+
+def run_layer(cfg, sd, x, device, index_mode="reference", table_dtype=None, scales=(None, None), max_tokens=None):
+    op = make_op(cfg, device, index_mode, max_tokens=max_tokens, table_dtype=table_dtype)
+    w = op_weights(sd, device, *scales)
+    T = x.shape[0] * x.shape[1]
+    xd = x.to(device).view(T, -1).contiguous()
+    out = torch.empty(T, cfg.output_dim, dtype=cfg.dtype, device=device)
+    ids = torch.empty(T, cfg.num_heads, cfg.top_k, dtype=torch.int64, device=device)
+    sc = torch.empty(T, cfg.num_heads, cfg.top_k, dtype=torch.float32, device=device)
+    op.forward(xd, w, out, ids, sc)
+    op.query_status()
+    return op, w, out, ids, sc
+
+
+# ---------------------------------------------------------------------------
+# whole layer against the reference's golden outputs
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["tiny_fp32", "c1", "c1_affine", "c2_slice", "c2_slice_affine"])
+def test_forward_matches_reference_golden(cuda_device, name):
+    cfg, sd, x, rec = load_golden(name)
+    op, w, out, ids, sc = run_layer(cfg, sd, x, cuda_device)
+    ref_ids = torch.from_numpy(rec["ids"].astype(np.int64)).view(-1, cfg.num_heads, cfg.top_k)
+    ref_sc = torch.from_numpy(rec["scores"]).view(-1, cfg.num_heads, cfg.top_k)
+    ref_out = torch.from_numpy(rec["out"]).view(-1, cfg.output_dim)
+    check_ids(ids, ref_ids, ref_sc, sc)
+    assert torch.allclose(sc.cpu(), ref_sc, rtol=0, atol=3e-6)
+    check_out(out, ref_out, cfg.dtype)
+    # duplicates inside a row must be preserved (the reference's i0+i1 ids collide)
+    assert sum(len(set(r)) < len(r) for r in ids.view(-1, cfg.top_k).tolist()) > 0 or name == "tiny_fp32"
+
+
+@pytest.mark.parametrize("name", ["tiny_fp32", "c1"])
+def test_product_index_mode_matches_oracle(cuda_device, name):
+    cfg, sd, x, rec = load_golden(name)
+    op, w, out, ids, sc = run_layer(cfg, sd, x, cuda_device, index_mode="product")
+    with torch.no_grad():
+        o_out, o_ids, o_sc = orc.forward(x.float(), oracle_weights(sd), oracle_shape(cfg), "product")
+    check_ids(ids, o_ids.view(ids.shape), o_sc.view(sc.shape), sc)
+    assert torch.equal(o_ids.view(ids.shape), torch.from_numpy(rec["ids_product"].astype(np.int64)).view(ids.shape))
+    check_out(out, o_out.view(out.shape), cfg.dtype)
+
+
+# ---------------------------------------------------------------------------
+# stages on their own
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["tiny_fp32", "c1_affine", "c2_slice_affine"])
+def test_query_projection_and_layernorm(cuda_device, name):
+    cfg, sd, x, rec = load_golden(name)
+    op = make_op(cfg, cuda_device)
+    w = op_weights(sd, cuda_device)
+    q = op.project_queries(x.to(cuda_device).view(cfg.tokens, -1).contiguous(), w)
+    with torch.no_grad():
+        ref = orc.make_queries(x.float(), oracle_weights(sd), oracle_shape(cfg)).view(q.shape)
+    assert torch.allclose(q.cpu(), ref, rtol=1e-5, atol=2e-5), float((q.cpu() - ref).abs().max())
+
+
+@pytest.mark.parametrize("mode", ["reference", "product"])
+@pytest.mark.parametrize("n_keys,k,H,Q", [((16, 16), 1, 1, 32), ((16, 16), 4, 2, 64), ((128, 128), 8, 4, 128),
+                                           ((128, 128), 16, 8, 256), ((1024, 1024), 16, 8, 256),
+                                           ((100, 36), 8, 3, 48), ((8, 8), 16, 2, 32)])
+def test_select_matches_reference_selection(cuda_device, mode, n_keys, k, H, Q):
+    """Mirrors tests/test_peer_selection.py:110-137 of the reference: shape, dtype, finiteness,
+    and here also the values."""
+    torch.manual_seed(1234 + k + H)
+    T = 77
+    q = torch.randn(1, T, H, Q)
+    keys = [torch.randn(n, Q // 2) * (Q // 2) ** -0.5 for n in n_keys]
+    cfg = syn.PeerConfig("sel", 64, 64, H, Q, n_keys, k, torch.float32, torch.float32, 1, T)
+    op = make_op(cfg, cuda_device, mode)
+    ids, sc = op.select(q.view(T, H, Q).to(cuda_device).contiguous(), keys[0].to(cuda_device), keys[1].to(cuda_device))
+    with torch.no_grad():
+        o_ids, o_sc = orc.select(q, keys, k, n_keys, index_mode=mode)
+    assert ids.shape == (T, H, k) and ids.dtype == torch.int64 and sc.dtype == torch.float32
+    assert torch.isfinite(sc).all()
+    check_ids(ids, o_ids.view(T, H, k), o_sc.view(T, H, k), sc, min_exact=0.99)
+    assert torch.allclose(sc.cpu(), o_sc.view(T, H, k), rtol=0, atol=3e-6)
+
+
+def test_select_with_duplicated_sub_keys_forces_exact_ties(cuda_device):
+    torch.manual_seed(5)
+    T, H, Q, n, k = 33, 2, 64, 32, 8
+    keys = [torch.randn(n, Q // 2) for _ in range(2)]
+    keys[0][7] = keys[0][3]; keys[0][20] = keys[0][3]; keys[1][9] = keys[1][1]
+    q = torch.randn(1, T, H, Q)
+    cfg = syn.PeerConfig("tie", 64, 64, H, Q, (n, n), k, torch.float32, torch.float32, 1, T)
+    op = make_op(cfg, cuda_device, "product")
+    ids, sc = op.select(q.view(T, H, Q).to(cuda_device).contiguous(), keys[0].to(cuda_device), keys[1].to(cuda_device))
+    with torch.no_grad():
+        o_ids, o_sc = orc.select(q, keys, k, (n, n), index_mode="product")
+    # scores are pinned exactly; ids may differ only inside exactly tied groups
+    assert torch.allclose(sc.cpu(), o_sc.view(T, H, k), rtol=0, atol=3e-6)
+    n_rows, exact, near, bad = orc.compare_selection(ids.cpu(), o_ids.view(T, H, k), o_sc.view(T, H, k), sc.cpu())
+    assert bad == 0
+    # and the kernel's own rule is deterministic: lower index first among equals
+    ids2, _ = op.select(q.view(T, H, Q).to(cuda_device).contiguous(), keys[0].to(cuda_device), keys[1].to(cuda_device))
+    assert torch.equal(ids, ids2)
+
+
+@pytest.mark.parametrize("dtype,D,Dout,H,k,N,T", [
+    (torch.float32, 32, 48, 2, 4, 64, 7), (torch.float32, 256, 256, 4, 8, 16384, 300),
+    (torch.bfloat16, 256, 512, 2, 4, 1000, 65), (torch.bfloat16, 2048, 2048, 8, 16, 4096, 200),
+    (torch.bfloat16, 1024, 2048, 4, 16, 513, 129), (torch.float32, 2048, 2048, 2, 8, 300, 19)])
+def test_gather_eval_from_given_selections(cuda_device, dtype, D, Dout, H, k, N, T):
+    torch.manual_seed(T)
+    U = (torch.randn(N, D) * D ** -0.5).to(dtype)
+    V = (torch.randn(N, Dout) * D ** -0.5).to(dtype)
+    x = torch.randn(1, T, D).to(dtype)
+    ids = torch.randint(0, N, (1, T, H, k))
+    ids[0, 0, 0, 0] = 0; ids[0, 0, 0, 1] = N - 1; ids[0, 1, 0, :] = 5      # edges and duplicates
+    sc = torch.randn(1, T, H, k)
+    # the operator only needs the expert-stage fields here; any key grid that multiplies to N will do
+    op = PeerOp(input_dim=D, output_dim=Dout, num_heads=H, query_dim=32, product_key_dim=(N, 1), top_k=k,
+                act_dtype=dtype, table_dtype=dtype, max_tokens=T, device=cuda_device)
+    wts = torch.softmax(sc, -1)
+    out = op.gather_eval(x.view(T, D).to(cuda_device), ids.view(T, H * k).to(torch.int32).to(cuda_device),
+                         wts.view(T, H * k).to(cuda_device).contiguous(), U.to(cuda_device), V.to(cuda_device))
+    op.query_status()
+    shape = orc.PeerShape(D, Dout, N, k, H, 1, 32, [N, 1])
+    w = orc.PeerWeights(None, None, None, None, [], U.float(), V.float())
+    with torch.no_grad():
+        ref = orc.evaluate_experts(x.float(), ids, sc, w, shape).view(T, Dout)
+    check_out(out, ref, dtype)
+
+
+def test_out_of_range_ids_are_reported_not_dereferenced(cuda_device):
+    D, H, k, N, T = 256, 2, 4, 64, 5
+    op = PeerOp(input_dim=D, output_dim=D, num_heads=H, query_dim=32, product_key_dim=(8, 8), top_k=k,
+                act_dtype=torch.float32, table_dtype=torch.float32, max_tokens=T, device=cuda_device)
+    U = torch.randn(N, D, device=cuda_device); V = torch.randn(N, D, device=cuda_device)
+    x = torch.randn(T, D, device=cuda_device)
+    ids = torch.randint(0, N, (T, H * k), dtype=torch.int32, device=cuda_device)
+    w = torch.full((T, H * k), 1.0 / k, device=cuda_device)
+    good = op.gather_eval(x, ids, w, U, V).clone()
+    op.query_status()
+    bad_ids = ids.clone(); bad_ids[2, 3] = N; bad_ids[4, 0] = -1
+    out = op.gather_eval(x, bad_ids, w, U, V)
+    with pytest.raises(RuntimeError, match="expert id"):
+        op.query_status()
+    op.query_status()                                   # the word is cleared by the read
+    assert torch.equal(out[[0, 1, 3]], good[[0, 1, 3]])  # untouched tokens are unaffected
+    assert torch.isfinite(out).all()
+
+
+# ---------------------------------------------------------------------------
+# module-level behaviour (mirrors the reference's integration tests)
+# ---------------------------------------------------------------------------
+def _module(cfg, sd, device, index_mode="reference"):
+    m = PEER(**cfg.module_kwargs()).to(cfg.dtype)
+    m.load_state_dict({k: v.to(cfg.dtype) for k, v in sd.items()})
+    m = m.to(device).eval()
+    m.index_mode = index_mode
+    return m
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_module_forward_shape_dtype_finite(cuda_device, dtype):
+    """tests/test_peer_integration.py:156-179 of the reference: B=4, S=16, output shape
+    [B,S,out], dtype preserved, no NaN/Inf; plus the tracker attributes (tracking.py:347-353)."""
+    cfg = syn.PeerConfig("m", 64, 96, 2, 32, (8, 8), 4, dtype, dtype, 4, 16)
+    sd = syn.make_weights(cfg, 3, "cpu", random_affine=True)
+    m = _module(cfg, sd, cuda_device)
+    x = syn.make_input(cfg, 3, cuda_device)
+    with torch.no_grad():
+        y = m(x)
+    assert y.shape == (4, 16, 96) and y.dtype == dtype and torch.isfinite(y).all()
+    assert m._last_expert_indices.shape == (4, 16, 2, 4) and m._last_expert_indices.dtype == torch.int64
+    assert m._last_expert_scores.shape == (4, 16, 2, 4)
+    with torch.no_grad():
+        ref, r_ids, r_sc = orc.forward(x.cpu().float(), oracle_weights(sd), oracle_shape(cfg))
+    check_ids(m._last_expert_indices.view(-1, 2, 4), r_ids.view(-1, 2, 4), r_sc.view(-1, 2, 4),
+              m._last_expert_scores.view(-1, 2, 4), min_exact=0.98)
+    check_out(y.view(-1, 96), ref.view(-1, 96), dtype)
+    # non-contiguous input, as a transformer block may hand over
+    xt = x.transpose(0, 1).contiguous().transpose(0, 1)
+    with torch.no_grad():
+        assert torch.equal(m(xt), y)
+
+
+def test_module_determinism_linearity_and_weight_updates(cuda_device):
+    cfg, sd, x, rec = load_golden("c1")
+    m = _module(cfg, sd, cuda_device)
+    xd = x.to(cuda_device)
+    with torch.no_grad():
+        y1 = m(xd).clone()
+        y2 = m(xd).clone()
+        assert torch.equal(y1, y2)                                   # bit-identical repeat
+        m.expert_up.weight.mul_(2.0)                                 # in-place update, no stale copy
+        y3 = m(xd).clone()
+        assert torch.allclose(y3, 2 * y1, rtol=1e-6, atol=1e-7)      # linear in V
+        m.expert_up.weight.mul_(0.5)
+        m.sub_keys[0].copy_(m.sub_keys[0].flip(0))                   # keys change -> selection changes
+        y4 = m(xd)
+        assert not torch.equal(y4, y1)
+        m.sub_keys[0].copy_(m.sub_keys[0].flip(0))
+        assert torch.equal(m(xd), y1)
+
+
+def test_functional_entry_point(cuda_device):
+    cfg, sd, x, rec = load_golden("c1_affine")
+    g = lambda k: sd[k].to(cuda_device)
+    y = peer_forward(x.to(cuda_device), g("query_proj.weight").view(cfg.num_heads, cfg.query_dim, -1),
+                     g("query_proj.bias"), g("sub_keys.0"), g("sub_keys.1"), g("expert_down.weight"),
+                     g("expert_up.weight"), cfg.num_heads, cfg.num_experts, 1, cfg.top_k,
+                     ln_weight=g("query_layer_norm.weight"), ln_bias=g("query_layer_norm.bias"))
+    assert y.shape == (cfg.batch, cfg.seq, cfg.output_dim)
+    check_out(y.view(-1, cfg.output_dim), torch.from_numpy(rec["out"]).view(-1, cfg.output_dim), cfg.dtype)
+
+
+def test_host_buffer_path_equals_device_path(cuda_device):
+    cfg = syn.scaled(syn.CONFIGS["c2"], product_key_dim=(64, 64), batch=3, seq=1111)
+    sd = syn.make_weights(cfg, 11, cuda_device)
+    m = _module(cfg, sd, cuda_device, "product")
+    x = syn.make_input(cfg, 11, "cpu").pin_memory()
+    with torch.no_grad():
+        y_dev = m(x.to(cuda_device))
+        ids_dev = m._last_expert_indices.clone()
+        y_host = m.forward_host(x)
+    assert y_host.device.type == "cpu" and y_host.shape == y_dev.shape
+    assert torch.equal(y_host, y_dev.cpu())
+    assert torch.equal(m._last_expert_indices, ids_dev.cpu())
+
+
+def test_slicing_by_max_tokens_is_transparent(cuda_device):
+    cfg, sd, x, rec = load_golden("c1")
+    _, _, out_a, ids_a, _ = run_layer(cfg, sd, x, cuda_device, max_tokens=256)
+    _, _, out_b, ids_b, _ = run_layer(cfg, sd, x, cuda_device, max_tokens=37)
+    assert torch.equal(out_a, out_b) and torch.equal(ids_a, ids_b)
+
+
+# ---------------------------------------------------------------------------
+# medium and full-size bf16 layers, product-key ids (tables really in HBM)
+# ---------------------------------------------------------------------------
+def _oracle_on_tokens(cfg, sd, x_dev, tok, mode, scales=(None, None)):
+    """fp32 oracle on selected tokens; tables stay in their storage dtype and only the
+    gathered rows are widened.  ``sd`` may live on either device."""
+    sd_cpu = {k: v.cpu() for k, v in sd.items()}
+    w = oracle_weights(sd_cpu, torch.float32, *[None if s is None else s.cpu() for s in scales], tables_as_stored=True)
+    xs = x_dev.view(-1, cfg.input_dim)[tok].cpu().float().unsqueeze(0)
+    with torch.no_grad():
+        return orc.forward(xs, w, oracle_shape(cfg), mode, token_chunk=64)
+
+
+@pytest.mark.parametrize("mode", ["reference", "product"])
+def test_bf16_medium_layer(cuda_device, mode):
+    cfg = syn.scaled(syn.CONFIGS["c2"], product_key_dim=(256, 256), batch=2, seq=300)
+    sd = syn.make_weights(cfg, 5, cuda_device, random_affine=True)
+    x = syn.make_input(cfg, 5, cuda_device)
+    op, w, out, ids, sc = run_layer(cfg, sd, x, cuda_device, mode)
+    tok = torch.arange(0, cfg.tokens, 3)
+    o_out, o_ids, o_sc = _oracle_on_tokens(cfg, sd, x, tok, mode)
+    check_ids(ids[tok.to(cuda_device)], o_ids[0], o_sc[0], sc[tok.to(cuda_device)])
+    check_out(out[tok.to(cuda_device)], o_out[0], cfg.dtype)
+
+
+def test_bf16_full_size_1m_experts(cuda_device):
+    """The 1,048,576-expert layer at its full batch: sampled tokens against the oracle, plus
+    size-independent properties (token-permutation equivariance, linearity in V)."""
+    cfg = syn.CONFIGS["c2"]
+    sd = syn.make_weights(cfg, 0, cuda_device)
+    x = syn.make_input(cfg, 0, cuda_device)
+    op, w, out, ids, sc = run_layer(cfg, sd, x, cuda_device, "product")
+    assert int(ids.max()) > 1_000_000 and int(ids.min()) >= 0
+    g = torch.Generator().manual_seed(0)
+    tok = torch.randperm(cfg.tokens, generator=g)[:192].sort().values
+    sd_cpu = {k: v.cpu() for k, v in sd.items()}
+    o_out, o_ids, o_sc = _oracle_on_tokens(cfg, sd_cpu, x, tok, "product")
+    check_ids(ids[tok.to(cuda_device)], o_ids[0], o_sc[0], sc[tok.to(cuda_device)])
+    check_out(out[tok.to(cuda_device)], o_out[0], cfg.dtype)
+    # permutation of tokens permutes the output rows, bit for bit
+    perm = torch.randperm(cfg.tokens, generator=g).to(cuda_device)
+    xp = x.view(cfg.tokens, -1)[perm].contiguous()
+    outp = torch.empty_like(out)
+    op.forward(xp, w, outp)
+    assert torch.equal(outp, out[perm])
+    # reference index mode on the same weights: ids stay below n0+n1-1
+    op2, w2, out2, ids2, sc2 = run_layer(cfg, sd, x, cuda_device, "reference")
+    assert int(ids2.max()) <= 2046
+    assert torch.equal(sc2, sc)
+    o_out2, o_ids2, o_sc2 = _oracle_on_tokens(cfg, sd_cpu, x, tok[:64], "reference")
+    check_out(out2[tok[:64].to(cuda_device)], o_out2[0], cfg.dtype)
+
+
+def test_fp8_tables(cuda_device):
+    cfg = syn.scaled(syn.CONFIGS["c3"], product_key_dim=(256, 256), batch=2, seq=257)
+    sd = syn.make_weights(cfg, 9, cuda_device)
+    x = syn.make_input(cfg, 9, cuda_device)
+    qd, sdn = syn.quantize_rows_e4m3(sd["expert_down.weight"])
+    qu, sup = syn.quantize_rows_e4m3(sd["expert_up.weight"])
+    sd8 = dict(sd); sd8["expert_down.weight"] = qd; sd8["expert_up.weight"] = qu
+    op, w, out, ids, sc = run_layer(cfg, sd8, x, cuda_device, "product", scales=(sdn, sup))
+    tok = torch.arange(0, cfg.tokens, 4)
+    # (i) kernel correctness: oracle on the dequantised tables, bf16 bound
+    o_out, o_ids, o_sc = _oracle_on_tokens(cfg, sd8, x, tok, "product", scales=(sdn, sup))
+    check_ids(ids[tok.to(cuda_device)], o_ids[0], o_sc[0], sc[tok.to(cuda_device)])
+    check_out(out[tok.to(cuda_device)], o_out[0], cfg.dtype)
+    # (ii) accuracy of FP8 storage itself: oracle on the original bf16 tables, looser bound
+    b_out, _, _ = _oracle_on_tokens(cfg, sd, x, tok, "product")
+    mx, l1 = orc.output_errors(out[tok.to(cuda_device)].cpu().float(), b_out[0].view(-1, cfg.output_dim))
+    assert mx <= 5e-2 and l1 <= 8e-2, (mx, l1)
