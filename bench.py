@@ -40,12 +40,13 @@ FALLBACK_HBM_GBS = 6650.0
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=["c2", "c3"])
     ap.add_argument("--index-mode", default="product", choices=["product", "reference"])
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per GPU (profiling of small cases)")
+    ap.add_argument("--keys", type=int, default=0, help="override sub-keys per dimension (profiling of small cases)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -63,7 +64,7 @@ def hbm_peak():
 
 
 class ClockSampler:
-    """nvidia-smi clock/throttle samples every 200 ms while the timed region runs."""
+    """nvidia-smi clock/throttle samples every 50 ms while the timed region runs."""
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -72,7 +73,7 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.p = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.Q,
-                                       "--format=csv,noheader,nounits", "-lms", "200"],
+                                       "--format=csv,noheader,nounits", "-lms", "50"],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
@@ -112,6 +113,8 @@ def build_cfg(args):
     cfg = syn.CONFIGS[args.config]
     if args.tokens:
         cfg = syn.scaled(cfg, batch=1, seq=args.tokens)
+    if args.keys:
+        cfg = syn.scaled(cfg, product_key_dim=(args.keys, args.keys))
     return cfg
 
 

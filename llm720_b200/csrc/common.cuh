@@ -21,7 +21,7 @@ constexpr int STATUS_TIMEOUT = 2;
 // Upper bound on the polls of one mbarrier wait.  Each poll is a try_wait
 // that itself blocks for a hardware-defined slice, so this is far more than
 // any real copy needs and still ends in well under a second.
-constexpr uint32_t WAIT_POLL_LIMIT = 1u << 22;
+constexpr uint32_t WAIT_POLL_LIMIT = 1u << 20;
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
