@@ -1,6 +1,7 @@
 // Internal launch interface between the C ABI (peer_api.cu) and the kernels.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -24,6 +25,34 @@ struct QueryArgs {
     int act_dtype;
 };
 cudaError_t launch_query_simt(const QueryArgs& a, cudaStream_t s);
+
+// Tensor-core (tcgen05) query stage for bf16 layers.  Besides the optional fp32 outputs of
+// QueryArgs it writes the normalised queries as three bf16 terms (hi, mid, lo), each a
+// [T, H, Q] array, `split_stride` elements apart.
+bool query_tc_supported(const QueryArgs& a);
+cudaError_t query_tc_setup();
+cudaError_t launch_query_tc(const QueryArgs& a, __nv_bfloat16* split_out, int64_t split_stride, int* status,
+                            int sm_count, cudaStream_t s);
+
+// Tensor-core (tcgen05) selection for bf16 layers: same results as launch_select_simt.
+struct SelectTcArgs {
+    const __nv_bfloat16* q_split;  // [3][term_rows, Q]: hi/mid/lo terms of the normalised queries
+    int64_t term_rows;             // rows between the three term arrays (>= rows)
+    const void* keys0;             // [n0, Q/2] bf16, as stored (not normalised)
+    const void* keys1;             // [n1, Q/2]
+    const float* invn0;            // [n0] 1/||key|| (or 1)
+    const float* invn1;            // [n1]
+    int64_t rows;                  // T * H
+    int Q, n0, n1, kp0, kp1, k, mult0, mult1;
+    int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores;   // as in SelectArgs
+    int* status;
+    int sm_count;
+};
+bool select_tc_supported(int act_dtype, int Q, int n0, int n1, int k, int kp0, int kp1);
+cudaError_t select_tc_setup();
+cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s);
+// out[j] = 1 / max(||keys[j]||, 1e-12), or 1 when !do_norm (bf16 keys)
+cudaError_t launch_key_inv_norms(const void* keys, int n, int width, int do_norm, float* out, cudaStream_t s);
 
 // rows of `width` elements -> fp32, each row divided by max(||row||, 1e-12) when do_norm;
 // written [rows, width], or [width, rows] when transpose_out

@@ -24,6 +24,11 @@ struct peer_op {
     float* khat0 = nullptr;       // [Q/2, n0] normalised sub-keys, transposed
     float* khat1 = nullptr;       // [Q/2, n1]
     float* q_hat = nullptr;       // [max_tokens, H, Q]
+    __nv_bfloat16* q_split = nullptr;   // [3][max_tokens, H, Q]: hi/mid/lo bf16 terms of q_hat (tensor-core path)
+    bool use_tc = false;          // bf16 layer whose shapes the tcgen05 query kernel covers
+    bool use_tc_select = false;   // ... and the tcgen05 select kernel
+    float* invn0 = nullptr;       // [n0] 1/||key|| (tensor-core select)
+    float* invn1 = nullptr;       // [n1]
     int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
     float* sel_w = nullptr;       // [max_tokens, H*k]
     uint16_t* pairs = nullptr;
@@ -77,7 +82,7 @@ static int candidates_per_dim(int top_k, int dim_size) {
 }
 
 static void free_all(peer_op* h) {
-    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->sel_ids);
+    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->sel_ids);
     cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status);
     for (int b = 0; b < 2; ++b) {
         cudaFree(h->d_x[b]); cudaFree(h->d_out[b]); cudaFree(h->d_ids[b]); cudaFree(h->d_sc[b]);
@@ -178,6 +183,19 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     alloc(reinterpret_cast<void**>(&h->khat0), sizeof(float) * hw * c->n_keys0);
     alloc(reinterpret_cast<void**>(&h->khat1), sizeof(float) * hw * c->n_keys1);
     alloc(reinterpret_cast<void**>(&h->q_hat), sizeof(float) * c->max_tokens * c->num_heads * c->query_dim);
+    {
+        QueryArgs probe{};
+        probe.act_dtype = c->act_dtype; probe.Q = c->query_dim; probe.D = c->input_dim;
+        h->use_tc = query_tc_supported(probe);
+    }
+    h->use_tc_select = h->use_tc && select_tc_supported(c->act_dtype, c->query_dim, c->n_keys0, c->n_keys1,
+                                                        h->k_final, h->kp0, h->kp1);
+    if (h->use_tc_select) {
+        alloc(reinterpret_cast<void**>(&h->invn0), sizeof(float) * c->n_keys0);
+        alloc(reinterpret_cast<void**>(&h->invn1), sizeof(float) * c->n_keys1);
+    }
+    if (h->use_tc)
+        alloc(reinterpret_cast<void**>(&h->q_split), sizeof(__nv_bfloat16) * 3 * c->max_tokens * c->num_heads * c->query_dim);
     alloc(reinterpret_cast<void**>(&h->sel_ids), sizeof(int32_t) * c->max_tokens * HK);
     alloc(reinterpret_cast<void**>(&h->sel_w), sizeof(float) * c->max_tokens * HK);
     alloc(reinterpret_cast<void**>(&h->pairs), sizeof(uint16_t) * MAX_PAIRS);
@@ -186,6 +204,8 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
     if (e == cudaSuccess) e = select_simt_setup();
     if (e == cudaSuccess) e = gather_eval_setup();
+    if (e == cudaSuccess && h->use_tc) e = query_tc_setup();
+    if (e == cudaSuccess && h->use_tc_select) e = select_tc_setup();
     if (e != cudaSuccess) {
         fail(nullptr, PEER_ERR_CUDA, "peer_create: %s", cudaGetErrorString(e));
         free_all(h);
@@ -231,6 +251,16 @@ static int normalise_keys(peer_op* h, const void* keys0, const void* keys1, cuda
     return PEER_OK;
 }
 
+// 1/||key|| per sub-key, for the tensor-core select kernel (which contracts with the keys as stored)
+static int key_inv_norms(peer_op* h, const void* keys0, const void* keys1, cudaStream_t s) {
+    const peer_config_t& c = h->cfg;
+    const int hw = c.query_dim / 2;
+    CU_TRY(h, launch_key_inv_norms(keys0, c.n_keys0, hw, c.norm_keys, h->invn0, s));
+    CU_TRY(h, launch_key_inv_norms(keys1, c.n_keys1, hw, c.norm_keys, h->invn1, s));
+    h->launches += 2;
+    return PEER_OK;
+}
+
 static SelectArgs select_args(peer_op* h, int64_t n_tokens) {
     const peer_config_t& c = h->cfg;
     SelectArgs a{};
@@ -247,7 +277,7 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     const peer_config_t& c = h->cfg;
     QueryArgs q{};
     q.x = x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
-    q.q_ln_out = nullptr; q.q_hat_out = h->q_hat; q.T = n; q.D = c.input_dim; q.H = c.num_heads;
+    q.q_ln_out = nullptr; q.q_hat_out = h->use_tc_select ? nullptr : h->q_hat; q.T = n; q.D = c.input_dim; q.H = c.num_heads;
     q.Q = c.query_dim; q.layer_norm = c.layer_norm; q.norm_query = c.norm_query; q.act_dtype = c.act_dtype;
     cudaEvent_t* ev = nullptr;
     if (h->timing) {
@@ -262,12 +292,25 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         h->tev_used += 4;
         CU_TRY(h, cudaEventRecord(ev[0], s));
     }
-    CU_TRY(h, launch_query_simt(q, s));
+    if (h->use_tc)
+        CU_TRY(h, launch_query_tc(q, h->q_split, c.max_tokens * c.num_heads * c.query_dim, h->status, h->sm_count, s));
+    else
+        CU_TRY(h, launch_query_simt(q, s));
     if (ev) CU_TRY(h, cudaEventRecord(ev[1], s));
 
-    SelectArgs sa = select_args(h, n);
-    sa.ids32 = h->sel_ids; sa.weights = h->sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
-    CU_TRY(h, launch_select_simt(sa, s));
+    if (h->use_tc_select) {
+        SelectTcArgs ta{};
+        ta.q_split = h->q_split; ta.term_rows = c.max_tokens * c.num_heads; ta.keys0 = t->keys0; ta.keys1 = t->keys1;
+        ta.invn0 = h->invn0; ta.invn1 = h->invn1; ta.rows = n * c.num_heads; ta.Q = c.query_dim;
+        ta.n0 = c.n_keys0; ta.n1 = c.n_keys1; ta.kp0 = h->kp0; ta.kp1 = h->kp1; ta.k = h->k_final;
+        ta.mult0 = h->mult0; ta.mult1 = h->mult1; ta.ids32 = h->sel_ids; ta.weights = h->sel_w;
+        ta.ids64 = ids_out; ta.raw_scores = scores_out; ta.status = h->status; ta.sm_count = h->sm_count;
+        CU_TRY(h, launch_select_tc(ta, s));
+    } else {
+        SelectArgs sa = select_args(h, n);
+        sa.ids32 = h->sel_ids; sa.weights = h->sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
+        CU_TRY(h, launch_select_simt(sa, s));
+    }
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], s));
 
     GatherArgs g{};
@@ -317,7 +360,7 @@ extern "C" int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_
     if (rc) return rc;
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = normalise_keys(h, t->keys0, t->keys1, s);
+    rc = h->use_tc_select ? key_inv_norms(h, t->keys0, t->keys1, s) : normalise_keys(h, t->keys0, t->keys1, s);
     if (rc) return rc;
     const int ab = act_bytes(c.act_dtype);
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
@@ -374,7 +417,8 @@ extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64
     dt.x = h->d_x[0]; dt.out = h->d_out[0];
     rc = check_tensors(h, &dt, true);
     if (rc) return rc;
-    rc = normalise_keys(h, t->keys0, t->keys1, h->st_run);
+    rc = h->use_tc_select ? key_inv_norms(h, t->keys0, t->keys1, h->st_run)
+                          : normalise_keys(h, t->keys0, t->keys1, h->st_run);
     if (rc) return rc;
 
     const int ab = act_bytes(c.act_dtype);
@@ -424,7 +468,10 @@ extern "C" int peer_project_queries(peer_handle_t h, const peer_tensors_t* t, in
     q.x = t->x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
     q.q_ln_out = queries_out; q.q_hat_out = nullptr; q.T = n_tokens; q.D = c.input_dim; q.H = c.num_heads;
     q.Q = c.query_dim; q.layer_norm = c.layer_norm; q.norm_query = c.norm_query; q.act_dtype = c.act_dtype;
-    CU_TRY(h, launch_query_simt(q, static_cast<cudaStream_t>(stream)));
+    if (h->use_tc)
+        CU_TRY(h, launch_query_tc(q, nullptr, 0, h->status, h->sm_count, static_cast<cudaStream_t>(stream)));
+    else
+        CU_TRY(h, launch_query_simt(q, static_cast<cudaStream_t>(stream)));
     h->launches += 1;
     return PEER_OK;
 }
