@@ -41,9 +41,9 @@ constexpr int BOX_BYTES = 128 * 64 * 2;   // one TMA box: 128 rows x 64 bf16
 constexpr int MAX_KA = 2;          // 64-column boxes per half (half width 64 or 128)
 constexpr int A_BYTES = 3 * MAX_KA * BOX_BYTES;     // 96 KB
 constexpr int B_STAGE_BYTES = MAX_KA * BOX_BYTES;   // 32 KB
-constexpr int B_STAGES = 3;
+constexpr int B_STAGES = 2;
 constexpr int N_ACC = 4;
-constexpr int QC = 16;             // queue entries per row and scan group
+constexpr int QC = 32;             // queue entries per row and scan group
 constexpr int LK = 16;             // list length kept per half
 constexpr int THREADS = 320;
 constexpr uint32_t TMEM_COLS = 512;
@@ -52,8 +52,9 @@ struct Smem {
     static constexpr size_t a_off = 0;
     static constexpr size_t b_off = a_off + A_BYTES;
     static constexpr size_t q_off = b_off + static_cast<size_t>(B_STAGES) * B_STAGE_BYTES;   // [2][QC][128] x 8 B
-    static constexpr size_t bar_off = q_off + 2 * QC * BM * 8;
-    static constexpr size_t total = bar_off + 32 * sizeof(uint64_t) + 16 + 1024;
+    static constexpr size_t tau_off = q_off + 2 * QC * BM * 8;                                 // [2][128] floats
+    static constexpr size_t bar_off = tau_off + 2 * BM * sizeof(float);
+    static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 16 + 1008;
 };
 
 struct SelTcParams {
@@ -108,7 +109,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::bar_off);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 32);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     const uint32_t sA = smem_u32(smem + Smem::a_off), sB = smem_u32(smem + Smem::b_off);
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t a_full = bar0, a_empty = bar0 + 8;
@@ -124,6 +125,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         mbar_fence_init();
         tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k0); tc::tma_prefetch_desc(&map_k1);
     }
+    float* tau_sh = reinterpret_cast<float*>(smem + Smem::tau_off);   // each group's current 16th-best score per row
+    if (tid < 2 * BM) tau_sh[tid] = -INFINITY;
     if (warp == 0) {
         __syncwarp();
         tc::tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -222,15 +225,21 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int i = 0; i < LK; ++i) { v[i] = -INFINITY; c[i] = 0x7fffffff; }
                 int cnt = 0;
                 float tau = -INFINITY;
+                // A score below the OTHER group's 16th-best cannot be among the row's 16 best either,
+                // so the two groups share their thresholds through shared memory.
+                volatile float* tau_mine = tau_sh + wg * BM + row;
+                volatile float* tau_other = tau_sh + (wg ^ 1) * BM + row;
                 auto drain = [&]() {
                     const int maxc = __reduce_max_sync(FULL_MASK, cnt);
                     for (int i = 0; i < maxc; ++i) {
                         float x = -INFINITY; int col = 0;
                         if (i < cnt) { const uint2 e = queue[i * BM + row]; x = __uint_as_float(e.x); col = static_cast<int>(e.y); }
+                        if (!__any_sync(FULL_MASK, x > v[LK - 1])) continue;
                         insert_pair(v, c, x, col);
                     }
                     cnt = 0;
-                    tau = v[LK - 1];
+                    *tau_mine = v[LK - 1];
+                    tau = fmaxf(v[LK - 1], *tau_other);
                 };
                 for (int ch = 0; ch < nch; ++ch, ++g) {
                     if ((g & 1u) != static_cast<uint32_t>(wg)) continue;
@@ -238,6 +247,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     if (ok && !mbar_wait(acc_full(acc), (g / N_ACC) & 1, p.status)) ok = false;
                     if (!ok) continue;
                     tc::fence_after_sync();
+                    tau = fmaxf(tau, *tau_other);
                     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * NC;
                     const int col0 = ch * NC;
 #pragma unroll 1
@@ -251,29 +261,33 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         }
                         const int cb = col0 + b * 32;
                         if (cb >= n) continue;
+                        if (cb + 32 <= n) {
 #pragma unroll
-                        for (int j8 = 0; j8 < 32; j8 += 8) {
-                            float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
-                            if (cb + j8 + 8 <= n) {
-                                s0 = __ldg(reinterpret_cast<const float4*>(invn + cb + j8));
-                                s1 = __ldg(reinterpret_cast<const float4*>(invn + cb + j8 + 4));
-                            } else {
-                                float t8[8];
+                            for (int j8 = 0; j8 < 32; j8 += 8) {
+                                const float4 s0 = __ldg(reinterpret_cast<const float4*>(invn + cb + j8));
+                                const float4 s1 = __ldg(reinterpret_cast<const float4*>(invn + cb + j8 + 4));
+                                const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) t8[e] = (cb + j8 + e < n) ? __ldg(invn + cb + j8 + e) : 0.f;
-                                s0 = make_float4(t8[0], t8[1], t8[2], t8[3]); s1 = make_float4(t8[4], t8[5], t8[6], t8[7]);
-                            }
-                            const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const int col = cb + j8 + e;
-                                const float x = (col < n) ? __uint_as_float(r[j8 + e]) * sc[e] : -INFINITY;
-                                if (x > tau) {
-                                    queue[cnt * BM + row] = make_uint2(__float_as_uint(x), static_cast<uint32_t>(col));
-                                    ++cnt;
+                                for (int e = 0; e < 8; ++e) {
+                                    // branch-free push: always store into the next free slot, keep it only if it passes
+                                    const float x = __uint_as_float(r[j8 + e]) * sc[e];
+                                    queue[cnt * BM + row] = make_uint2(__float_as_uint(x), static_cast<uint32_t>(cb + j8 + e));
+                                    cnt += (x > tau) ? 1 : 0;
                                 }
+                                if (__any_sync(FULL_MASK, cnt > QC - 8)) drain();
                             }
-                            if (__any_sync(FULL_MASK, cnt > QC - 8)) drain();
+                        } else {                       // ragged last batch of the table
+#pragma unroll
+                            for (int j8 = 0; j8 < 32; j8 += 8) {
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) {
+                                    const int col = cb + j8 + e;
+                                    const float x = (col < n) ? __uint_as_float(r[j8 + e]) * __ldg(invn + col) : -INFINITY;
+                                    queue[cnt * BM + row] = make_uint2(__float_as_uint(x), static_cast<uint32_t>(col));
+                                    cnt += (x > tau) ? 1 : 0;
+                                }
+                                if (__any_sync(FULL_MASK, cnt > QC - 8)) drain();
+                            }
                         }
                     }
                 }
@@ -285,6 +299,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         queue[i * BM + row] = make_uint2(__float_as_uint(v[i]), static_cast<uint32_t>(c[i]));
                 }
                 asm volatile("bar.sync 2, 256;" ::: "memory");
+                *tau_mine = -INFINITY;                 // both groups are done scanning this half
                 uint2 oth[LK];
                 if (merger) {
 #pragma unroll
