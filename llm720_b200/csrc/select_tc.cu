@@ -17,7 +17,7 @@
 //   warp 0      TMA producer: the query tile of a half (3 terms), then the
 //               key chunks (128 keys) through a ring;
 //   warp 1      MMA issuer: 128x128 accumulators, four in flight in TMEM;
-//   warps 2-5   scan group 0, warps 6-9 scan group 1: thread = TMEM lane =
+//   warps 4-7   scan group 0, warps 8-11 scan group 1 (warps 2-3 idle): thread = TMEM lane =
 //               one row; the groups take alternate chunks.  A thread filters
 //               its row's scores against its current 16th-best value, queues
 //               the survivors in shared memory and, when a queue runs full,
@@ -45,7 +45,8 @@ constexpr int B_STAGES = 2;
 constexpr int N_ACC = 4;
 constexpr int QC = 32;             // queue entries per row and scan group
 constexpr int LK = 16;             // list length kept per half
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;       // warps 0-3: TMA, MMA, two idle; warps 4-7 and 8-11: the scan groups
+constexpr int CTRL_REGS = 40, SCAN_REGS = 232;   // 128*40 + 256*232 = 384*168 registers
 constexpr uint32_t TMEM_COLS = 512;
 
 struct Smem {
@@ -142,7 +143,10 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int64_t n_tiles = (p.rows + BM - 1) / BM;
     const uint32_t a_bytes = 3u * KA * BOX_BYTES, b_bytes = static_cast<uint32_t>(KA) * BOX_BYTES;
 
-    if (warp == 0) {
+    // The control warps need few registers; the rest of the launch allocation goes to the scan groups.
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CTRL_REGS));
+      if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
             uint32_t a_phase = 0; int stage = 0; uint32_t b_phase = 0; bool ok = true;
@@ -167,7 +171,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const uint32_t idesc = tc::idesc_bf16_f32(BM, NC);
@@ -202,9 +206,11 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
         }
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SCAN_REGS));
         // ---------------- scan groups ----------------
-        const int wg = (warp - 2) >> 2;               // 0 or 1
+        const int wg = (warp - 4) >> 2;               // 0 or 1
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
         uint2* queue = reinterpret_cast<uint2*>(smem + Smem::q_off) + static_cast<size_t>(wg) * QC * BM;   // [QC][128]
