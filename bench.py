@@ -35,6 +35,11 @@ sys.path.insert(0, ROOT)
 METRIC = "PEER-layer tokens/sec @1M experts"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes moved by the expert-stage kernel per algorithmic byte, from one ncu capture of a smaller
+# case of the same kernel (4096 tokens, 262,144 experts; dram__bytes_read.sum + dram__bytes_write.sum =
+# 4.150 GB for 4.295 GB of algorithmic bytes; profiles/gather_eval_bf16_d2048_small_case.md).  Traffic
+# grows in proportion to the tokens, so the bench scales it to its own launch size.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bfloat16": 0.966}
 
 
 def parse():
@@ -276,7 +281,9 @@ def main():
     achieved = gathered / (g_ms / 1e3) / 1e9
     roofline = {"bound": "hbm", "kernel": "gather_eval_kernel (expert stage)", "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                "traffic": None, "ms_per_launch": g_ms,
+                "traffic": (NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(workload["table_dtype"]) or 0) * gathered or None,
+                "traffic_note": "ncu capture of a smaller case of the same kernel, scaled by tokens",
+                "ms_per_launch": g_ms,
                 "algorithmic_bytes_per_launch": gathered,
                 "stage_ms_per_step": {"query": ms_q / max(n_slices, 1), "select": ms_s / max(n_slices, 1),
                                       "experts": g_ms}}
