@@ -136,6 +136,21 @@ int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* ids, const f
                      const void* expert_down, const void* expert_up, const float* down_scale,
                      const float* up_scale, void* out, int64_t n_tokens, void* stream);
 
+/* Product-key retrieval (same result as peer_select) for callers that cannot allocate device
+ * memory: no handle, no cudaMalloc anywhere on this path.  This entry point has no counterpart in
+ * the reference; it exists for embedders that have given all GPU memory to their own pool, or that
+ * run in a loop where an allocation's device-wide synchronisation is not acceptable.  The scratch
+ * the kernels need sits in an 8 MiB array inside the library image (held by every GPU that loads
+ * the library), so n_tokens*num_heads*query_dim*4 + (n_keys0+n_keys1)*query_dim*2 bytes must fit
+ * in it; larger calls return PEER_ERR_UNSUPPORTED with both sizes in peer_last_error(NULL).
+ * Of `cfg` only abi_version, num_heads, query_dim, n_keys0, n_keys1, top_k, norm_keys, norm_query,
+ * act_dtype (dtype of the sub-keys) and index_mode are read.  The first call on each device does
+ * a one-time set-up (address of the array, kernel attribute): make it at start-up, before any
+ * stream capture.  All calls share the array: calls whose kernels may overlap on the GPU race. */
+int peer_select_noalloc(const peer_config_t* cfg, const float* queries, const void* keys0,
+                        const void* keys1, int64_t n_tokens, int64_t* ids_out, float* scores_out,
+                        void* stream);
+
 /* Reads and clears the device status word (synchronises `stream`).  Returns
  * PEER_OK, PEER_ERR_DEVICE_TIMEOUT or PEER_ERR_BOUNDS.  The kernels never
  * trap: a bounded wait that runs out, or an expert id outside the table,

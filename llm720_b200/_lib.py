@@ -43,6 +43,8 @@ EXPORTS = {
     "peer_project_queries": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                               C.c_void_p, C.c_void_p]),
+    "peer_select_noalloc": (C.c_int, [C.POINTER(PeerConfig), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
+                                      C.c_void_p, C.c_void_p]),
     "peer_gather_eval": (C.c_int, [C.c_void_p] * 9 + [C.c_int64, C.c_void_p]),
     "peer_query_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "peer_launch_count": (C.c_int64, [C.c_void_p]),

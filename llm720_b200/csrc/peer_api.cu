@@ -68,6 +68,11 @@ static int fail(peer_op* h, int code, const char* fmt, ...) {
             return fail(h, PEER_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
     } while (0)
 
+namespace peer {
+// used by entry points that have no handle to hang an error text on
+void set_global_error(const char* msg) { g_create_error = msg ? msg : ""; }
+}  // namespace peer
+
 static int act_bytes(int dt) { return dt == PEER_DTYPE_F32 ? 4 : (dt == PEER_DTYPE_BF16 ? 2 : 1); }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -80,6 +85,8 @@ static int candidates_per_dim(int top_k, int dim_size) {
     if (kp > dim_size) kp = dim_size;
     return kp < 1 ? 1 : kp;
 }
+
+namespace peer { int candidates_per_dim_2d(int top_k, int dim_size) { return candidates_per_dim(top_k, dim_size); } }
 
 static void free_all(peer_op* h) {
     cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->sel_ids);
