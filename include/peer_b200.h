@@ -136,6 +136,18 @@ int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* ids, const f
                      const void* expert_down, const void* expert_up, const float* down_scale,
                      const float* up_scale, void* out, int64_t n_tokens, void* stream);
 
+/* Expert evaluation against a ROW SHARD of the tables (expert-parallel layers): the caller holds
+ * rows [r0, r0 + n_local_rows) of expert_down / expert_up, `ids` are LOCAL row numbers, token t uses
+ * its first counts[t] (<= entries_per_token) entries, and the result is the fp32 partial sum
+ * out_f32[t] = sum_j w[t,j] * act(down[ids[t,j]] . x[t]) * up[ids[t,j]] that the ranks then reduce.
+ * The reference has no sharded implementation of the layer (expert sharding is announced in
+ * docs/paper/paper.tex:446 and listed as future work in docs/CUTLASS_KERNEL.md:181); this is the
+ * per-rank piece of it, with the semantics of experts.py:332-382 restricted to the owned rows. */
+int peer_gather_eval_partial(peer_handle_t h, const void* x, const int32_t* ids, const float* weights,
+                             const int32_t* counts, int32_t entries_per_token, const void* expert_down,
+                             const void* expert_up, const float* down_scale, const float* up_scale,
+                             int64_t n_local_rows, float* out_f32, int64_t n_tokens, void* stream);
+
 /* Product-key retrieval (same result as peer_select) for callers that cannot allocate device
  * memory: no handle, no cudaMalloc anywhere on this path.  This entry point has no counterpart in
  * the reference; it exists for embedders that have given all GPU memory to their own pool, or that

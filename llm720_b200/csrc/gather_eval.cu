@@ -107,6 +107,8 @@ struct GatherParams {
     const char* down; const char* up; const float* down_scale; const float* up_scale;
     void* out; int64_t T; int HK; int64_t N; int D, Dout; int activation; int* status;
     int nch_u, nch_v;          // 16-byte chunks per down / up row
+    const int32_t* counts;     // optional [T]: entries of token t that are in use (<= HK)
+    float* out_f32;            // optional [T, Dout] fp32 output instead of `out`
 };
 
 template <typename XT, typename TT, int CH>
@@ -140,7 +142,6 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
     const uint32_t row_u = static_cast<uint32_t>(p.nch_u) * 16u, row_v = static_cast<uint32_t>(p.nch_v) * 16u;
     const XT* __restrict__ xg = static_cast<const XT*>(p.x);
     XT* __restrict__ og = static_cast<XT*>(p.out);
-    const int total_rows = 2 * p.HK;
 
     int slot = 0;            // next ring slot to consume
     uint32_t parity = 0;     // its phase
@@ -150,7 +151,9 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
     for (int64_t t = static_cast<int64_t>(blockIdx.x) * WARPS + warp; t < p.T && alive; t += nwarps) {
         // ---- token prologue: selections into shared memory, x into registers
         __syncwarp();
-        for (int e = lane; e < p.HK; e += 32) {
+        const int hk = p.counts ? min(max(p.counts[t], 0), p.HK) : p.HK;
+        const int total_rows = 2 * hk;
+        for (int e = lane; e < hk; e += 32) {
             int32_t id = p.ids[t * p.HK + e];
             float w = p.weights[t * p.HK + e];
             if (static_cast<uint32_t>(id) >= static_cast<uint64_t>(p.N)) {
@@ -160,16 +163,35 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
             s_id[e] = id; s_w[e] = w;
             if (SCALED) { s_us[e] = __ldg(p.down_scale + id); s_vs[e] = __ldg(p.up_scale + id); }
         }
-        float xr[CH * EPC];
+        // The activation row stays in registers for the whole token: fp32, or (rows longer than 64
+        // elements per lane, bf16 activations) as packed bf16 pairs widened at each use.
+        constexpr bool PACKX = (CH * EPC > 64);
+        static_assert(!PACKX || sizeof(XT) == 2, "long rows need bf16 activations");
+        float xr[PACKX ? 1 : CH * EPC];
+        uint32_t xp[PACKX ? CH * EPC / 2 : 1];
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
             const int c = lane + 32 * i;
-            if (c < p.nch_u) XIo<XT, EPC>::load(xg + t * p.D + c * EPC, xr + i * EPC);
-            else {
+            if constexpr (PACKX) {
 #pragma unroll
-                for (int e = 0; e < EPC; ++e) xr[i * EPC + e] = 0.f;
+                for (int e = 0; e < EPC / 2; e += 4) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (c < p.nch_u) v = __ldg(reinterpret_cast<const uint4*>(xg + t * p.D + c * EPC + 2 * e));
+                    xp[i * EPC / 2 + e] = v.x; xp[i * EPC / 2 + e + 1] = v.y;
+                    xp[i * EPC / 2 + e + 2] = v.z; xp[i * EPC / 2 + e + 3] = v.w;
+                }
+            } else {
+                if (c < p.nch_u) XIo<XT, EPC>::load(xg + t * p.D + c * EPC, xr + i * EPC);
+                else {
+#pragma unroll
+                    for (int e = 0; e < EPC; ++e) xr[i * EPC + e] = 0.f;
+                }
             }
         }
+        auto xval = [&](int idx) -> float {
+            if constexpr (PACKX) return (idx & 1) ? bf16_hi(xp[idx >> 1]) : bf16_lo(xp[idx >> 1]);
+            else return xr[idx];
+        };
         float acc[CH * EPC];
 #pragma unroll
         for (int i = 0; i < CH * EPC; ++i) acc[i] = 0.f;
@@ -193,7 +215,7 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
             }
         }
 
-        for (int e = 0; e < p.HK; ++e) {
+        for (int e = 0; e < hk; ++e) {
             // ---- down row: dot with x
             if (!mbar_wait(bars_a + 8 * slot, parity, p.status)) { alive = false; }
             alive = __all_sync(FULL_MASK, alive);
@@ -210,8 +232,8 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
                         Chunk<TT>::decode(raw, f);
 #pragma unroll
                         for (int q = 0; q < EPC; q += 2) {
-                            d0 = fmaf(f[q], xr[i * EPC + q], d0);
-                            d1 = fmaf(f[q + 1], xr[i * EPC + q + 1], d1);
+                            d0 = fmaf(f[q], xval(i * EPC + q), d0);
+                            d1 = fmaf(f[q + 1], xval(i * EPC + q + 1), d1);
                         }
                     }
                 }
@@ -252,7 +274,16 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
 #pragma unroll
         for (int i = 0; i < CH; ++i) {
             const int c = lane + 32 * i;
-            if (c < p.nch_v) XIo<XT, EPC>::store(og + t * p.Dout + c * EPC, acc + i * EPC);
+            if (c < p.nch_v) {
+                if (p.out_f32) {
+#pragma unroll
+                    for (int q = 0; q < EPC; q += 4)
+                        *reinterpret_cast<float4*>(p.out_f32 + t * p.Dout + c * EPC + q) =
+                            make_float4(acc[i * EPC + q], acc[i * EPC + q + 1], acc[i * EPC + q + 2], acc[i * EPC + q + 3]);
+                } else {
+                    XIo<XT, EPC>::store(og + t * p.Dout + c * EPC, acc + i * EPC);
+                }
+            }
         }
     }
 }
@@ -284,14 +315,15 @@ cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
 template <typename XT, typename TT>
 cudaError_t launch_ch(const GatherArgs& a, const GatherParams& p, int max_ch, cudaStream_t s) {
     const int need = (max_ch + 31) / 32;     // chunks per lane
-    constexpr int EPL_LIMIT = 64;            // activation + accumulator registers per lane
+    // elements per lane: 64 with fp32 activations in registers, 128 with packed bf16 activations
     constexpr int EPC = Chunk<TT>::N;
+    constexpr int EPL_LIMIT = sizeof(XT) == 2 ? 128 : 64;
     if (need * EPC > EPL_LIMIT && need > 1) return cudaErrorInvalidValue;
     if (need <= 1) return launch_t<XT, TT, 1>(a, p, s);
     if (need <= 2) return launch_t<XT, TT, 2>(a, p, s);
     if (need <= 4) return launch_t<XT, TT, 4>(a, p, s);
-    if constexpr (EPC <= 8) { if (need <= 8) return launch_t<XT, TT, 8>(a, p, s); }
-    if constexpr (EPC <= 4) { if (need <= 16) return launch_t<XT, TT, 16>(a, p, s); }
+    if constexpr (8 * EPC <= EPL_LIMIT) { if (need <= 8) return launch_t<XT, TT, 8>(a, p, s); }
+    if constexpr (16 * EPC <= EPL_LIMIT) { if (need <= 16) return launch_t<XT, TT, 16>(a, p, s); }
     return cudaErrorInvalidValue;
 }
 
@@ -308,6 +340,7 @@ cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
     p.down_scale = a.down_scale; p.up_scale = a.up_scale; p.out = a.out; p.T = a.T; p.HK = a.HK;
     p.N = a.N; p.D = a.D; p.Dout = a.Dout; p.activation = a.activation; p.status = a.status;
     p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
+    p.counts = a.counts; p.out_f32 = a.out_f32;
     const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
     if (a.act_dtype == PEER_DTYPE_F32 && a.table_dtype == PEER_DTYPE_F32)
         return launch_ch<float, float>(a, p, max_ch, s);

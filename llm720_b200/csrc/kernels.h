@@ -96,6 +96,8 @@ struct GatherArgs {
     int act_dtype, table_dtype, activation;
     int* status;              // device status word
     int sm_count;
+    const int32_t* counts;    // optional [T]: how many of token t's HK entries are in use
+    float* out_f32;           // optional fp32 output [T, Dout] (partial sums of a row-sharded table)
 };
 cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s);
 // one-time per-process attribute set-up (dynamic shared memory opt-in)

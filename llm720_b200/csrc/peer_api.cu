@@ -533,6 +533,36 @@ extern "C" int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* i
     return PEER_OK;
 }
 
+extern "C" int peer_gather_eval_partial(peer_handle_t h, const void* x, const int32_t* ids, const float* weights,
+                                        const int32_t* counts, int32_t entries_per_token, const void* expert_down,
+                                        const void* expert_up, const float* down_scale, const float* up_scale,
+                                        int64_t n_local_rows, float* out_f32, int64_t n_tokens, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    const peer_config_t& c = h->cfg;
+    if (!x || !ids || !weights || !counts || !expert_down || !expert_up || !out_f32)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_partial: null pointer");
+    if (entries_per_token <= 0 || n_local_rows <= 0 || n_local_rows > c.num_experts)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_partial: entries_per_token and n_local_rows must be positive, rows <= num_experts");
+    if (c.table_dtype == PEER_DTYPE_E4M3 && (!down_scale || !up_scale))
+        return fail(h, PEER_ERR_INVALID_ARG, "FP8 tables need down_scale and up_scale");
+    if (!aligned16(x) || !aligned16(expert_down) || !aligned16(expert_up) || !aligned16(out_f32))
+        return fail(h, PEER_ERR_INVALID_ARG, "x, tables and out must be 16-byte aligned");
+    GatherArgs g{};
+    g.x = x; g.ids = ids; g.weights = weights; g.down = expert_down; g.up = expert_up;
+    g.down_scale = down_scale; g.up_scale = up_scale; g.out = out_f32; g.out_f32 = out_f32; g.counts = counts;
+    g.T = n_tokens; g.HK = entries_per_token; g.N = n_local_rows; g.D = c.input_dim; g.Dout = c.output_dim;
+    g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
+    g.status = h->status; g.sm_count = h->sm_count;
+    cudaError_t e = launch_gather_eval(g, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue)
+        return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or %d entries per token, is not implemented",
+                    c.input_dim, c.output_dim, entries_per_token);
+    CU_TRY(h, e);
+    h->launches += 1;
+    return PEER_OK;
+}
+
 extern "C" int peer_query_status(peer_handle_t h, void* stream) {
     if (!h) return PEER_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -178,6 +178,25 @@ class PeerOp:
                                                   _stream(self.device)))
         return out
 
+    def gather_eval_partial(self, x, ids32, weights, counts, down, up, down_scale=None, up_scale=None):
+        """Partial expert evaluation against a row shard: ids are LOCAL row numbers, token t uses its first
+        counts[t] entries; returns the fp32 partial sums [T, D_out]."""
+        self._dev(x, "x", self.act_dtype)
+        self._dev(ids32, "ids", torch.int32)
+        self._dev(weights, "weights", torch.float32)
+        self._dev(counts, "counts", torch.int32)
+        self._dev(down, "expert_down", self.table_dtype)
+        self._dev(up, "expert_up", self.table_dtype)
+        self._dev(down_scale, "down_scale", torch.float32)
+        self._dev(up_scale, "up_scale", torch.float32)
+        T, cap = ids32.shape
+        out = torch.empty(T, self.cfg.output_dim, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_gather_eval_partial(
+                self.handle, _ptr(x), _ptr(ids32), _ptr(weights), _ptr(counts), cap, _ptr(down), _ptr(up),
+                _ptr(down_scale), _ptr(up_scale), down.shape[0], _ptr(out), T, _stream(self.device)))
+        return out
+
     def query_status(self):
         """Synchronise and raise if a kernel recorded a timeout or an out-of-range id."""
         with torch.cuda.device(self.device):

@@ -1,0 +1,168 @@
+"""Expert-parallel PEER: the expert tables are split by rows over the ranks of a process group.
+
+The reference has no distributed PEER (its multi-GPU story is data parallelism through
+Accelerate, llm/training/train.py:472-476, 638-640; expert sharding is announced in
+docs/paper/paper.tex:446 and listed as future work in docs/CUTLASS_KERNEL.md:181).  This is
+the layer for tables that do not fit, or should not be replicated, on every GPU:
+
+  rank r owns rows [r*N/G, (r+1)*N/G) of expert_down / expert_up; the small weights (query
+  projection, LayerNorm, sub-keys) are replicated; every rank brings its own tokens.
+
+  1. all-gather of the activations (every owner needs x_t for the tuples it will receive);
+  2. each rank selects for ITS tokens (query projection + product-key retrieval kernels);
+  3. the selected (token, expert id, weight) tuples are bucketed by owner and exchanged with one
+     all-to-all (counts first, then the packed tuples);
+  4. each rank evaluates the tuples it received against its row shard (one kernel, fp32 partial
+     sums per token);
+  5. reduce-scatter of the partial sums gives every rank the outputs of its own tokens.
+
+Result: identical to the single-device layer on the concatenated batch, up to fp32 summation
+order.  The exchange logic (`route_tuples`, `pack_received`) is plain tensor code that runs on
+any device, so it is tested with CPU ranks over gloo; the kernels run on CUDA only.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def rows_per_rank(num_experts: int, world: int) -> int:
+    if num_experts % world:
+        raise ValueError(f"{num_experts} experts do not split evenly over {world} ranks")
+    return num_experts // world
+
+
+def route_tuples(ids: torch.Tensor, weights: torch.Tensor, token_offset: int, rows: int, world: int):
+    """ids int64/int32 [T, HK], weights fp32 [T, HK] of this rank's tokens ->
+    (send int32 [n, 3] = (global token, local row, weight bits) sorted by destination rank,
+     send_counts int64 [world])."""
+    T, HK = ids.shape
+    flat = ids.reshape(-1).to(torch.int64)
+    owner = torch.div(flat, rows, rounding_mode="floor")
+    order = torch.argsort(owner, stable=True)
+    tok = (torch.arange(T, device=ids.device, dtype=torch.int64).repeat_interleave(HK) + token_offset)[order]
+    local = (flat - owner * rows)[order]
+    wbits = weights.reshape(-1).to(torch.float32).view(torch.int32)[order]
+    send = torch.stack([tok.to(torch.int32), local.to(torch.int32), wbits], dim=1).contiguous()
+    counts = torch.bincount(owner, minlength=world)[:world]
+    return send, counts
+
+
+def pack_received(recv: torch.Tensor, n_tokens: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Received tuples int32 [m, 3] (any order) -> per-token padded lists:
+    (ids int32 [T, cap], weights fp32 [T, cap], counts int32 [T]); cap = the longest list (>= 1)."""
+    dev = recv.device
+    if recv.shape[0] == 0:
+        z = torch.zeros(n_tokens, 1, dtype=torch.int32, device=dev)
+        return z, torch.zeros(n_tokens, 1, dtype=torch.float32, device=dev), torch.zeros(n_tokens, dtype=torch.int32, device=dev)
+    tok = recv[:, 0].to(torch.int64)
+    order = torch.argsort(tok, stable=True)
+    tok = tok[order]
+    counts = torch.bincount(tok, minlength=n_tokens)
+    cap = max(int(counts.max()), 1)
+    start = torch.cumsum(counts, 0) - counts
+    pos = torch.arange(tok.numel(), device=dev) - start[tok]
+    ids = torch.zeros(n_tokens, cap, dtype=torch.int32, device=dev)
+    w = torch.zeros(n_tokens, cap, dtype=torch.float32, device=dev)
+    ids[tok, pos] = recv[order, 1]
+    w[tok, pos] = recv[order, 2].contiguous().view(torch.float32)
+    return ids, w, counts.to(torch.int32)
+
+
+def exchange(send: torch.Tensor, send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    """All-to-all of variable-length tuple buckets: counts first, then the tuples."""
+    world = dist.get_world_size(group)
+    recv_counts = torch.empty_like(send_counts)
+    dist.all_to_all_single(recv_counts, send_counts, group=group)
+    sc, rc = send_counts.tolist(), recv_counts.tolist()
+    recv = torch.empty(sum(rc), 3, dtype=torch.int32, device=send.device)
+    dist.all_to_all_single(recv, send, output_split_sizes=rc, input_split_sizes=sc, group=group)
+    return recv
+
+
+def reduce_scatter_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
+    """[T_total, D] fp32 partial sums -> this rank's [T_total/world, D] slice of the sum."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    t_local = partial.shape[0] // world
+    if dist.get_backend(group) == "nccl":
+        out = torch.empty(t_local, partial.shape[1], dtype=partial.dtype, device=partial.device)
+        dist.reduce_scatter_tensor(out, partial.contiguous(), group=group)
+        return out
+    dist.all_reduce(partial, group=group)        # CPU test backends without reduce-scatter
+    return partial[rank * t_local:(rank + 1) * t_local].clone()
+
+
+def sharded_forward(x_local: torch.Tensor, select_fn: Callable, eval_fn: Callable, num_experts: int,
+                    group=None) -> torch.Tensor:
+    """x_local [T_local, D] (same T_local on every rank) -> fp32 [T_local, D_out].
+
+    select_fn(x_local) -> (ids [T_local, HK] global expert ids, weights fp32 [T_local, HK]);
+    eval_fn(x_all [T, D], ids int32 [T, cap], weights [T, cap], counts int32 [T]) -> fp32 [T, D_out]
+    evaluated against this rank's row shard (ids are local row numbers)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    rows = rows_per_rank(num_experts, world)
+    t_local = x_local.shape[0]
+    x_all = torch.empty(world * t_local, x_local.shape[1], dtype=x_local.dtype, device=x_local.device)
+    dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=group)
+    ids, w = select_fn(x_local)
+    send, counts = route_tuples(ids, w, rank * t_local, rows, world)
+    recv = exchange(send, counts, group)
+    p_ids, p_w, p_cnt = pack_received(recv, world * t_local)
+    partial = eval_fn(x_all, p_ids, p_w, p_cnt)
+    return reduce_scatter_rows(partial, group)
+
+
+class ShardedPEER:
+    """The expert-parallel layer on the CUDA kernels.  `layer` is a `PEER` module whose small
+    weights are replicated and whose expert tables hold only this rank's rows
+    (`expert_down.weight` / `expert_up.weight` of shape [num_experts/world, D]);
+    `num_experts` and `product_key_dim` describe the FULL table."""
+
+    def __init__(self, layer, group=None):
+        self.layer, self.group = layer, group
+        self.world = dist.get_world_size(group)
+        self.rows = rows_per_rank(layer.num_experts, self.world)
+        if layer.expert_down.weight.shape[0] != self.rows:
+            raise ValueError(f"this rank must hold {self.rows} table rows, has {layer.expert_down.weight.shape[0]}")
+
+    @classmethod
+    def build(cls, module_kwargs: dict, small_weights: dict, down_local: torch.Tensor, up_local: torch.Tensor,
+              group=None, index_mode: str = "product", down_scale=None, up_scale=None):
+        """Assemble the layer from replicated small weights (state-dict names of the module) and this
+        rank's table rows, without ever materialising the full tables."""
+        from .peer import PEER
+        with torch.device("meta"):
+            layer = PEER(**module_kwargs)
+        layer.expert_down = torch.nn.Embedding(down_local.shape[0], down_local.shape[1], _weight=down_local)
+        layer.expert_up = torch.nn.Embedding(up_local.shape[0], up_local.shape[1], _weight=up_local)
+        layer.load_state_dict({k: v for k, v in small_weights.items() if not k.startswith("expert_")},
+                              strict=False, assign=True)
+        layer.expert_down_scale, layer.expert_up_scale = down_scale, up_scale
+        layer.eval().requires_grad_(False)
+        layer.index_mode = index_mode
+        return cls(layer, group)
+
+    @torch.no_grad()
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        L = self.layer
+        B, S, D = hidden_states.shape
+        x = hidden_states.contiguous().view(B * S, D)
+        w = L._weights()
+        op = L._operator(x.device, x.dtype, B * S * self.world)
+
+        def select_fn(xl):
+            q = op.project_queries(xl, w)
+            ids, raw = op.select(q, w["keys0"], w["keys1"])
+            T = xl.shape[0]
+            return ids.view(T, -1), torch.softmax(raw, dim=-1).view(T, -1)
+
+        def eval_fn(x_all, p_ids, p_w, p_cnt):
+            return op.gather_eval_partial(x_all, p_ids.contiguous(), p_w.contiguous(), p_cnt, w["expert_down"],
+                                          w["expert_up"], w["down_scale"], w["up_scale"])
+
+        out = sharded_forward(x, select_fn, eval_fn, L.num_experts, self.group)
+        return out.to(hidden_states.dtype).view(B, S, -1)
+
+    __call__ = forward

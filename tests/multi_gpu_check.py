@@ -1,0 +1,75 @@
+"""Two-or-more-GPU check of the expert-parallel layer, run under torchrun:
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29611 tests/multi_gpu_check.py
+
+Every rank holds a row shard of the tables of a decode-shaped layer (d_model 4096, 16 heads,
+query_dim 256, top-k 16, product-key ids); the result must equal the single-device layer that
+rank 0 evaluates on the concatenated batch with the full tables.  Also times the sharded step.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from llm720_b200 import PEER, synthetic as syn          # noqa: E402
+from llm720_b200.sharded import ShardedPEER              # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group("nccl", device_id=dev)
+    keys = int(os.environ.get("CHECK_KEYS", "256"))
+    cfg = syn.scaled(syn.CONFIGS["c4"], product_key_dim=(keys, keys), batch=64, seq=1)
+    sd = syn.make_weights(cfg, 4, dev, random_affine=True)          # same seed: identical on every rank
+    x = syn.make_input(cfg, 4, dev)                                 # [64, 1, 4096]
+    rows = cfg.num_experts // world
+    t_local = cfg.tokens // world
+    layer = ShardedPEER.build(cfg.module_kwargs(), sd, sd["expert_down.weight"][rank * rows:(rank + 1) * rows].contiguous(),
+                              sd["expert_up.weight"][rank * rows:(rank + 1) * rows].contiguous())
+    xl = x.view(cfg.tokens, 1, -1)[rank * t_local:(rank + 1) * t_local].contiguous()
+    out = layer(xl)
+    layer.layer._op.query_status()
+
+    with torch.device("meta"):
+        full = PEER(**cfg.module_kwargs())
+    full.load_state_dict(sd, assign=True)
+    full.eval().requires_grad_(False)
+    full.index_mode = "product"
+    with torch.no_grad():
+        ref = full(x)[rank * t_local:(rank + 1) * t_local]
+    err = float((out.float() - ref.float()).abs().max())
+    mag = float(ref.float().abs().max())
+    ok = torch.tensor([1 if err <= 2e-2 else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+
+    # timing: per-layer latency of the sharded step (max over ranks, CUDA events)
+    for _ in range(5):
+        layer(xl)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier(); torch.cuda.synchronize()
+    e0.record()
+    steps = 20
+    for _ in range(steps):
+        layer(xl)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(f"sharded PEER x{world}: experts {cfg.num_experts}, tokens {cfg.tokens}, max-abs err {err:.3g} "
+              f"(|ref| max {mag:.3g}), {float(ms):.3f} ms/step, {cfg.tokens / float(ms) * 1e3:.0f} tokens/s, "
+              f"{'OK' if int(ok) else 'MISMATCH'}")
+    dist.destroy_process_group()
+    sys.exit(0 if int(ok) else 1)
+
+
+if __name__ == "__main__":
+    main()

@@ -336,3 +336,49 @@ def test_fp8_tables(cuda_device):
     b_out, _, _ = _oracle_on_tokens(cfg, sd, x, tok, "product")
     mx, l1 = orc.output_errors(out[tok.to(cuda_device)].cpu().float(), b_out[0].view(-1, cfg.output_dim))
     assert mx <= 5e-2 and l1 <= 8e-2, (mx, l1)
+
+
+@pytest.mark.parametrize("dtype_name", ["bf16", "fp8"])
+def test_decode_shaped_layer_d4096(cuda_device, dtype_name):
+    """d_model 4096, 16 heads (256 row pairs per token), 64 single tokens: the long-row
+    instances of the expert stage (activations kept as packed bf16 pairs)."""
+    cfg = syn.scaled(syn.CONFIGS["c4"], product_key_dim=(128, 128), batch=64, seq=1)
+    sd = syn.make_weights(cfg, 13, cuda_device, random_affine=True)
+    x = syn.make_input(cfg, 13, cuda_device)
+    scales = (None, None)
+    sdk = dict(sd)
+    td = None
+    if dtype_name == "fp8":
+        sdk["expert_down.weight"], s0 = syn.quantize_rows_e4m3(sd["expert_down.weight"])
+        sdk["expert_up.weight"], s1 = syn.quantize_rows_e4m3(sd["expert_up.weight"])
+        scales, td = (s0, s1), torch.float8_e4m3fn
+    op, w, out, ids, sc = run_layer(cfg, sdk, x, cuda_device, "product", table_dtype=td, scales=scales)
+    tok = torch.arange(0, cfg.tokens, 2)
+    o_out, o_ids, o_sc = _oracle_on_tokens(cfg, sdk, x, tok, "product", scales=scales)
+    check_ids(ids[tok.to(cuda_device)], o_ids[0], o_sc[0], sc[tok.to(cuda_device)])
+    check_out(out[tok.to(cuda_device)], o_out[0], cfg.dtype)
+
+
+def test_partial_evaluation_against_a_row_shard(cuda_device):
+    """peer_gather_eval_partial: local row ids, per-token counts, fp32 partial sums."""
+    torch.manual_seed(3)
+    D, H, k, N, T, rows = 1024, 2, 8, 4096, 40, 512
+    op = PeerOp(input_dim=D, output_dim=D, num_heads=H, query_dim=32, product_key_dim=(64, 64), top_k=k,
+                act_dtype=torch.bfloat16, table_dtype=torch.bfloat16, max_tokens=T, device=cuda_device)
+    U = (torch.randn(rows, D) * D ** -0.5).bfloat16(); V = (torch.randn(rows, D) * D ** -0.5).bfloat16()
+    x = torch.randn(T, D).bfloat16()
+    cap = 11
+    ids = torch.randint(0, rows, (T, cap), dtype=torch.int32)
+    w = torch.rand(T, cap)
+    cnt = torch.randint(0, cap + 1, (T,), dtype=torch.int32); cnt[0] = 0; cnt[1] = cap
+    out = op.gather_eval_partial(x.to(cuda_device), ids.to(cuda_device), w.to(cuda_device), cnt.to(cuda_device),
+                                 U.to(cuda_device), V.to(cuda_device))
+    op.query_status()
+    ref = torch.zeros(T, D)
+    for t in range(T):
+        for j in range(int(cnt[t])):
+            r = int(ids[t, j])
+            ref[t] += w[t, j] * torch.nn.functional.gelu(U[r].float() @ x[t].float()) * V[r].float()
+    assert out.dtype == torch.float32
+    assert torch.allclose(out.cpu(), ref, rtol=1e-4, atol=1e-5), float((out.cpu() - ref).abs().max())
+    assert float(out[0].abs().max()) == 0.0
