@@ -281,7 +281,7 @@ def _oracle_on_tokens(cfg, sd, x_dev, tok, mode, scales=(None, None)):
 
 @pytest.mark.parametrize("mode", ["reference", "product"])
 def test_bf16_medium_layer(cuda_device, mode):
-    cfg = syn.scaled(syn.CONFIGS["c2"], product_key_dim=(256, 256), batch=2, seq=300)
+    cfg = syn.scaled(syn.CONFIGS["c2"], product_key_dim=(512, 640), batch=2, seq=300)
     sd = syn.make_weights(cfg, 5, cuda_device, random_affine=True)
     x = syn.make_input(cfg, 5, cuda_device)
     op, w, out, ids, sc = run_layer(cfg, sd, x, cuda_device, mode)
