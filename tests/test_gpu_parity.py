@@ -382,3 +382,43 @@ def test_partial_evaluation_against_a_row_shard(cuda_device):
     assert out.dtype == torch.float32
     assert torch.allclose(out.cpu(), ref, rtol=1e-4, atol=1e-5), float((out.cpu() - ref).abs().max())
     assert float(out[0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("opts", [dict(activation="relu"), dict(batch_norm_query=False), dict(norm_keys=False),
+                                  dict(norm_query=False), dict(norm_keys=False, norm_query=False, batch_norm_query=False)])
+def test_constructor_options(cuda_device, dtype, opts):
+    """relu and the three normalisation switches of the reference constructor (experts.py:55-60),
+    on the CUDA-core (fp32) and tensor-core (bf16) paths."""
+    cfg = syn.PeerConfig("opt", 256, 256, 4, 128, (128, 256), 8, dtype, dtype, 1, 150)
+    sd = syn.make_weights(cfg, 17, "cpu", random_affine=True)
+    x = syn.make_input(cfg, 17, "cpu")
+    kw = dict(cfg.module_kwargs(), **opts)
+    m = PEER(**kw).to(dtype)
+    state = {k: v.to(dtype) for k, v in sd.items() if not (k.startswith("query_layer_norm") and not kw["batch_norm_query"])}
+    m.load_state_dict(state)
+    m = m.to(cuda_device).eval()
+    m.index_mode = "product"
+    with torch.no_grad():
+        y = m(x.to(cuda_device))
+    okw = dict(kw); okw.pop("dropout")
+    shape = orc.PeerShape(**okw)
+    w = oracle_weights(sd)
+    if not kw["batch_norm_query"]:
+        w.ln_w = w.ln_b = None
+    with torch.no_grad():
+        ref, r_ids, r_sc = orc.forward(x.float(), w, shape, "product")
+    check_ids(m._last_expert_indices.view(-1, 4, 8), r_ids.view(-1, 4, 8), r_sc.view(-1, 4, 8),
+              m._last_expert_scores.view(-1, 4, 8), min_exact=0.98)
+    check_out(y.view(-1, 256), ref.view(-1, 256), dtype)
+
+
+def test_empty_and_single_token_inputs(cuda_device):
+    cfg, sd, x, rec = load_golden("c1")
+    m = _module(cfg, sd, cuda_device)
+    with torch.no_grad():
+        y0 = m(torch.empty(0, 5, cfg.input_dim, device=cuda_device))
+        y1 = m(x[:1, :1].to(cuda_device))
+        yall = m(x.to(cuda_device))
+    assert y0.shape == (0, 5, cfg.output_dim)
+    assert torch.equal(y1[0, 0], yall[0, 0])
