@@ -82,6 +82,58 @@ def exchange(send: torch.Tensor, send_counts: torch.Tensor, group=None) -> torch
     return recv
 
 
+# ---------------------------------------------------------------------------
+# Fixed-shape variant of the exchange: every rank sends every peer a bucket of the same capacity
+# (T_local*HK tuples, the worst case; 24 KB per peer at 8 tokens x 256 entries), unused slots carry
+# token -1.  One all-to-all, no counts to exchange, no host synchronisation, shapes that never change
+# from step to step.
+# ---------------------------------------------------------------------------
+def route_tuples_static(ids: torch.Tensor, weights: torch.Tensor, token_offset: int, rows: int, world: int) -> torch.Tensor:
+    """-> int32 [world, T*HK, 3] buckets of (global token | -1, local row, weight bits)."""
+    T, HK = ids.shape
+    n = T * HK
+    dev = ids.device
+    flat = ids.reshape(-1).to(torch.int64)
+    owner = torch.div(flat, rows, rounding_mode="floor")
+    order = torch.argsort(owner, stable=True)
+    owner_s = owner[order]
+    # fixed-size histogram (torch.bincount would read its bin count back to the host)
+    counts = torch.zeros(world, dtype=torch.int64, device=dev).scatter_add_(0, owner, torch.ones_like(owner))
+    start = torch.cumsum(counts, 0) - counts
+    pos = torch.arange(n, device=dev) - start[owner_s]
+    tok = (torch.arange(T, device=dev, dtype=torch.int64).repeat_interleave(HK) + token_offset)[order]
+    send = torch.full((world, n, 3), -1, dtype=torch.int32, device=dev)
+    send[owner_s, pos, 0] = tok.to(torch.int32)
+    send[owner_s, pos, 1] = (flat - owner * rows)[order].to(torch.int32)
+    send[owner_s, pos, 2] = weights.reshape(-1).to(torch.float32).view(torch.int32)[order]
+    return send
+
+
+def exchange_static(send: torch.Tensor, group=None) -> torch.Tensor:
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv
+
+
+def pack_received_static(recv: torch.Tensor, n_tokens: int, cap: int):
+    """Buckets int32 [world, m, 3] with -1 padding -> (ids int32 [T, cap], weights fp32 [T, cap],
+    counts int32 [T]); cap must be at least the longest per-token list (HK always is)."""
+    dev = recv.device
+    flat = recv.reshape(-1, 3)
+    tok = flat[:, 0].to(torch.int64)
+    key = torch.where(tok >= 0, tok, torch.full_like(tok, n_tokens))      # padding sorts behind every token
+    order = torch.argsort(key, stable=True)
+    key_s = key[order]
+    counts = torch.zeros(n_tokens + 1, dtype=torch.int64, device=dev).scatter_add_(0, key_s, torch.ones_like(key_s))
+    start = torch.cumsum(counts, 0) - counts
+    pos = torch.clamp(torch.arange(key_s.numel(), device=dev) - start[key_s], max=cap - 1)
+    ids = torch.zeros(n_tokens + 1, cap, dtype=torch.int32, device=dev)    # row T collects the padding
+    w = torch.zeros(n_tokens + 1, cap, dtype=torch.float32, device=dev)
+    ids[key_s, pos] = flat[order, 1]
+    w[key_s, pos] = flat[order, 2].contiguous().view(torch.float32)
+    return ids[:n_tokens], w[:n_tokens], torch.clamp(counts[:n_tokens], max=cap).to(torch.int32)
+
+
 def reduce_scatter_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
     """[T_total, D] fp32 partial sums -> this rank's [T_total/world, D] slice of the sum."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -95,7 +147,7 @@ def reduce_scatter_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
 
 
 def sharded_forward(x_local: torch.Tensor, select_fn: Callable, eval_fn: Callable, num_experts: int,
-                    group=None) -> torch.Tensor:
+                    group=None, static_shapes: bool = True) -> torch.Tensor:
     """x_local [T_local, D] (same T_local on every rank) -> fp32 [T_local, D_out].
 
     select_fn(x_local) -> (ids [T_local, HK] global expert ids, weights fp32 [T_local, HK]);
@@ -107,9 +159,13 @@ def sharded_forward(x_local: torch.Tensor, select_fn: Callable, eval_fn: Callabl
     x_all = torch.empty(world * t_local, x_local.shape[1], dtype=x_local.dtype, device=x_local.device)
     dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=group)
     ids, w = select_fn(x_local)
-    send, counts = route_tuples(ids, w, rank * t_local, rows, world)
-    recv = exchange(send, counts, group)
-    p_ids, p_w, p_cnt = pack_received(recv, world * t_local)
+    if static_shapes:
+        recv = exchange_static(route_tuples_static(ids, w, rank * t_local, rows, world), group)
+        p_ids, p_w, p_cnt = pack_received_static(recv, world * t_local, ids.shape[1])
+    else:
+        send, counts = route_tuples(ids, w, rank * t_local, rows, world)
+        recv = exchange(send, counts, group)
+        p_ids, p_w, p_cnt = pack_received(recv, world * t_local)
     partial = eval_fn(x_all, p_ids, p_w, p_cnt)
     return reduce_scatter_rows(partial, group)
 

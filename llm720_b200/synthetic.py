@@ -97,7 +97,7 @@ def _table(rows: int, width: int, std: float, dtype: torch.dtype, device, seed: 
 
 
 def make_weights(cfg: PeerConfig, seed: int = 0, device="cpu", table_rows: Optional[int] = None,
-                 random_affine: bool = False) -> Dict[str, torch.Tensor]:
+                 random_affine: bool = False, tables: bool = True) -> Dict[str, torch.Tensor]:
     """State-dict of a synthetic layer.  Small weights ~ N(0, 1/fan_in) in
     ``cfg.dtype``; query bias 0 and LayerNorm affine (1, 0) unless
     ``random_affine``; tables ~ N(0, 1/fan_in).  With an FP8 table type the
@@ -121,10 +121,20 @@ def make_weights(cfg: PeerConfig, seed: int = 0, device="cpu", table_rows: Optio
     half = Q // 2
     sd["sub_keys.0"] = (rn(n0, half) * half ** -0.5).to(cfg.dtype)
     sd["sub_keys.1"] = (rn(n1, half) * half ** -0.5).to(cfg.dtype)
+    if not tables:
+        return sd
     rows = cfg.num_experts if table_rows is None else min(table_rows, cfg.num_experts)
     sd["expert_down.weight"] = _table(rows, D, D ** -0.5, cfg.table_dtype, device, seed, 1)
     sd["expert_up.weight"] = _table(rows, Do, D ** -0.5, cfg.table_dtype, device, seed, 2)
     return sd
+
+
+def make_table_shard(cfg: PeerConfig, which: str, row_start: int, rows: int, seed: int = 0, device="cpu") -> torch.Tensor:
+    """Rows [row_start, row_start+rows) of `expert_down` / `expert_up` exactly as make_weights would
+    generate them (row_start must be a multiple of 65,536), without building the whole table."""
+    tensor_id = {"expert_down": 1, "expert_up": 2}[which]
+    width = cfg.input_dim if which == "expert_down" else cfg.output_dim
+    return _table(rows, width, cfg.input_dim ** -0.5, cfg.table_dtype, device, seed, tensor_id, row_start)
 
 
 def make_input(cfg: PeerConfig, seed: int = 0, device="cpu") -> torch.Tensor:

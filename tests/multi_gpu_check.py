@@ -28,26 +28,35 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     keys = int(os.environ.get("CHECK_KEYS", "256"))
     cfg = syn.scaled(syn.CONFIGS["c4"], product_key_dim=(keys, keys), batch=64, seq=1)
-    sd = syn.make_weights(cfg, 4, dev, random_affine=True)          # same seed: identical on every rank
+    compare = keys <= 512            # larger tables: only this rank's shard is ever built, timing only
+    sd = syn.make_weights(cfg, 4, dev, random_affine=True, tables=compare)   # same seed: identical on every rank
     x = syn.make_input(cfg, 4, dev)                                 # [64, 1, 4096]
     rows = cfg.num_experts // world
     t_local = cfg.tokens // world
-    layer = ShardedPEER.build(cfg.module_kwargs(), sd, sd["expert_down.weight"][rank * rows:(rank + 1) * rows].contiguous(),
-                              sd["expert_up.weight"][rank * rows:(rank + 1) * rows].contiguous())
+    if compare:
+        down = sd["expert_down.weight"][rank * rows:(rank + 1) * rows].contiguous()
+        up = sd["expert_up.weight"][rank * rows:(rank + 1) * rows].contiguous()
+    else:
+        down = syn.make_table_shard(cfg, "expert_down", rank * rows, rows, 4, dev)
+        up = syn.make_table_shard(cfg, "expert_up", rank * rows, rows, 4, dev)
+    layer = ShardedPEER.build(cfg.module_kwargs(), sd, down, up)
     xl = x.view(cfg.tokens, 1, -1)[rank * t_local:(rank + 1) * t_local].contiguous()
     out = layer(xl)
     layer.layer._op.query_status()
 
-    with torch.device("meta"):
-        full = PEER(**cfg.module_kwargs())
-    full.load_state_dict(sd, assign=True)
-    full.eval().requires_grad_(False)
-    full.index_mode = "product"
-    with torch.no_grad():
-        ref = full(x)[rank * t_local:(rank + 1) * t_local]
-    err = float((out.float() - ref.float()).abs().max())
-    mag = float(ref.float().abs().max())
-    ok = torch.tensor([1 if err <= 2e-2 else 0], device=dev)
+    err = mag = 0.0
+    if compare:
+        with torch.device("meta"):
+            full = PEER(**cfg.module_kwargs())
+        full.load_state_dict(sd, assign=True)
+        full.eval().requires_grad_(False)
+        full.index_mode = "product"
+        with torch.no_grad():
+            ref = full(x)[rank * t_local:(rank + 1) * t_local]
+        err = float((out.float() - ref.float()).abs().max())
+        mag = float(ref.float().abs().max())
+    finite = bool(torch.isfinite(out.float()).all()) and float(out.float().abs().max()) > 0
+    ok = torch.tensor([1 if (err <= 2e-2 and finite) else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
 
     # timing: per-layer latency of the sharded step (max over ranks, CUDA events)
@@ -64,7 +73,8 @@ def main():
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     if rank == 0:
-        print(f"sharded PEER x{world}: experts {cfg.num_experts}, tokens {cfg.tokens}, max-abs err {err:.3g} "
+        print(f"sharded PEER x{world}: experts {cfg.num_experts}, tokens {cfg.tokens}, "
+              f"{'compared with the single-device layer: ' if compare else 'timing only; '}max-abs err {err:.3g} "
               f"(|ref| max {mag:.3g}), {float(ms):.3f} ms/step, {cfg.tokens / float(ms) * 1e3:.0f} tokens/s, "
               f"{'OK' if int(ok) else 'MISMATCH'}")
     dist.destroy_process_group()

@@ -19,7 +19,7 @@ def _cpu_layer():
     return cfg, syn.make_weights(cfg, 21, "cpu", random_affine=True), syn.make_input(cfg, 21, "cpu")
 
 
-def _rank_main(rank, world, port, result_q):
+def _rank_main(rank, world, port, result_q, static_shapes=True):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -46,7 +46,7 @@ def _rank_main(rank, world, port, result_q):
                     out[t] += wt[t, j] * torch.nn.functional.gelu(U[r] @ x_all[t]) * V[r]
             return out
 
-        out = sharded.sharded_forward(x_local, select_fn, eval_fn, cfg.num_experts)
+        out = sharded.sharded_forward(x_local, select_fn, eval_fn, cfg.num_experts, static_shapes=static_shapes)
         ref, _, _ = orc.forward(x, w, shape, "product")
         ref = ref.view(cfg.tokens, -1)[rank * t_local:(rank + 1) * t_local]
         result_q.put((rank, float((out - ref).abs().max()), float(ref.abs().max())))
@@ -54,11 +54,12 @@ def _rank_main(rank, world, port, result_q):
         dist.destroy_process_group()
 
 
-def test_two_cpu_ranks_equal_single_device():
+@pytest.mark.parametrize("static_shapes", [True, False])
+def test_two_cpu_ranks_equal_single_device(static_shapes):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + os.getpid() % 2000
-    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q)) for r in range(2)]
+    port = 29500 + os.getpid() % 2000 + int(static_shapes)
+    procs = [ctx.Process(target=_rank_main, args=(r, 2, port, q, static_shapes)) for r in range(2)]
     [p.start() for p in procs]
     res = [q.get(timeout=180) for _ in procs]
     [p.join(60) for p in procs]
@@ -91,6 +92,25 @@ def test_route_and_pack_roundtrip():
         assert exp == have
     e_ids, e_w, e_cnt = sharded.pack_received(torch.empty(0, 3, dtype=torch.int32), 3)
     assert e_ids.shape == (3, 1) and int(e_cnt.sum()) == 0
+
+
+def test_static_route_and_pack_match_the_dynamic_ones():
+    torch.manual_seed(1)
+    T, HK, world, rows = 6, 8, 4, 16
+    ids = torch.randint(0, world * rows, (T, HK))
+    ids[2] = 5                                      # one token sends everything to one owner
+    w = torch.rand(T, HK)
+    send = sharded.route_tuples_static(ids, w, 0, rows, world)
+    assert send.shape == (world, T * HK, 3)
+    for owner in range(world):
+        bucket = send[owner:owner + 1]
+        a_ids, a_w, a_cnt = sharded.pack_received_static(bucket, T, HK)
+        dyn = bucket[0][bucket[0, :, 0] >= 0]
+        b_ids, b_w, b_cnt = sharded.pack_received(dyn, T)
+        assert torch.equal(a_cnt, b_cnt)
+        for t in range(T):
+            n = int(a_cnt[t])
+            assert sorted(zip(a_ids[t, :n].tolist(), a_w[t, :n].tolist())) == sorted(zip(b_ids[t, :n].tolist(), b_w[t, :n].tolist()))
 
 
 def test_uneven_split_is_rejected():
