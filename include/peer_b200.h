@@ -108,7 +108,9 @@ int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, voi
 /* Same, with t->x and t->out (and the optional ids/scores outputs) in HOST
  * memory (pinned for full speed): token slices are copied in, processed and
  * copied out on three internal streams so transfers overlap the kernels.
- * Returns after the last slice has landed in t->out.  Replaces the
+ * Returns after the last slice has landed in t->out.  The call runs on the library's own streams: work
+ * the caller enqueued earlier on another stream (an in-place weight update, say) must have completed
+ * before the call.  Replaces the
  * host-tensor call path of peer_forward_cutlass
  * (llm/models/kernels/peer_cutlass.py:135-234). */
 int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens);

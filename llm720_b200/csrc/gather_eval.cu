@@ -299,12 +299,15 @@ template <typename XT, typename TT, int CH>
 cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
     const size_t smem = smem_bytes<XT, TT, CH>(a.HK);
     if (smem > MAX_SMEM) return cudaErrorInvalidValue;
-    static bool configured = false;     // per instantiation; the attribute is sticky per function
-    if (!configured) {
+    static bool configured[64] = {};    // per instantiation and device; the attribute is sticky per function
+    int dev = 0;
+    cudaError_t de = cudaGetDevice(&dev);
+    if (de != cudaSuccess) return de;
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
         if (e != cudaSuccess) return e;
-        configured = true;
+        if (dev >= 0 && dev < 64) configured[dev] = true;
     }
     int64_t ctas = (a.T + WARPS - 1) / WARPS;
     if (ctas > a.sm_count) ctas = a.sm_count;

@@ -136,6 +136,9 @@ class PeerOp:
         if x.device.type != "cpu" or out.device.type != "cpu":
             raise RuntimeError("forward_host takes host tensors for x and out")
         t = self._tensors(x, w, out, ids_out, scores_out, host_io=True)
+        # the library runs this call on its own streams: make earlier work of the caller's stream
+        # (a weight update, for instance) visible first
+        torch.cuda.current_stream(self.device).synchronize()
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_forward_host(self.handle, C.byref(t), x.shape[0]))
 
