@@ -47,6 +47,8 @@ struct SelectTcArgs {
     int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores;   // as in SelectArgs
     int* status;
     int sm_count;
+    int32_t* overflow_rows;        // [rows]: rows the kernel leaves to the exact kernel (clustered scores)
+    int* overflow_count;           // device counter, zeroed by the caller before the launch
 };
 bool select_tc_supported(int act_dtype, int Q, int n0, int n1, int k, int kp0, int kp1);
 cudaError_t select_tc_setup();
@@ -77,6 +79,12 @@ struct SelectArgs {
     float* weights;       // optional [rows, k] softmax over k
     int64_t* ids64;       // optional [rows, k]
     float* raw_scores;    // optional [rows, k]
+    // optional: process only the rows row_list[0 .. *row_count) (device memory), and/or take the
+    // normalised queries as the sum of three bf16 terms split_stride elements apart
+    const int32_t* row_list;
+    const int* row_count;
+    const __nv_bfloat16* q_split;
+    int64_t split_stride;
 };
 cudaError_t launch_select_simt(const SelectArgs& a, cudaStream_t s);
 

@@ -29,6 +29,8 @@ struct peer_op {
     bool use_tc_select = false;   // ... and the tcgen05 select kernel
     float* invn0 = nullptr;       // [n0] 1/||key|| (tensor-core select)
     float* invn1 = nullptr;       // [n1]
+    int32_t* ovf_rows = nullptr;  // [max_tokens*H] rows the tensor-core select leaves to the exact kernel
+    int* ovf_count = nullptr;
     int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
     float* sel_w = nullptr;       // [max_tokens, H*k]
     uint16_t* pairs = nullptr;
@@ -89,7 +91,7 @@ static int candidates_per_dim(int top_k, int dim_size) {
 namespace peer { int candidates_per_dim_2d(int top_k, int dim_size) { return candidates_per_dim(top_k, dim_size); } }
 
 static void free_all(peer_op* h) {
-    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->sel_ids);
+    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->ovf_rows); cudaFree(h->ovf_count); cudaFree(h->sel_ids);
     cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status);
     for (int b = 0; b < 2; ++b) {
         cudaFree(h->d_x[b]); cudaFree(h->d_out[b]); cudaFree(h->d_ids[b]); cudaFree(h->d_sc[b]);
@@ -200,6 +202,8 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     if (h->use_tc_select) {
         alloc(reinterpret_cast<void**>(&h->invn0), sizeof(float) * c->n_keys0);
         alloc(reinterpret_cast<void**>(&h->invn1), sizeof(float) * c->n_keys1);
+        alloc(reinterpret_cast<void**>(&h->ovf_rows), sizeof(int32_t) * c->max_tokens * c->num_heads);
+        alloc(reinterpret_cast<void**>(&h->ovf_count), sizeof(int));
     }
     if (h->use_tc)
         alloc(reinterpret_cast<void**>(&h->q_split), sizeof(__nv_bfloat16) * 3 * c->max_tokens * c->num_heads * c->query_dim);
@@ -312,7 +316,16 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         ta.n0 = c.n_keys0; ta.n1 = c.n_keys1; ta.kp0 = h->kp0; ta.kp1 = h->kp1; ta.k = h->k_final;
         ta.mult0 = h->mult0; ta.mult1 = h->mult1; ta.ids32 = h->sel_ids; ta.weights = h->sel_w;
         ta.ids64 = ids_out; ta.raw_scores = scores_out; ta.status = h->status; ta.sm_count = h->sm_count;
+        ta.overflow_rows = h->ovf_rows; ta.overflow_count = h->ovf_count;
+        CU_TRY(h, cudaMemsetAsync(h->ovf_count, 0, sizeof(int), s));
         CU_TRY(h, launch_select_tc(ta, s));
+        // rows whose candidate lists overflowed (none for ordinary data) are redone exactly
+        SelectArgs fx = select_args(h, n);
+        fx.q_hat = nullptr; fx.q_split = h->q_split; fx.split_stride = c.max_tokens * c.num_heads * c.query_dim;
+        fx.row_list = h->ovf_rows; fx.row_count = h->ovf_count;
+        fx.ids32 = h->sel_ids; fx.weights = h->sel_w; fx.ids64 = ids_out; fx.raw_scores = scores_out;
+        CU_TRY(h, launch_select_simt(fx, s));
+        h->launches += 1;
     } else {
         SelectArgs sa = select_args(h, n);
         sa.ids32 = h->sel_ids; sa.weights = h->sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
@@ -367,7 +380,8 @@ extern "C" int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_
     if (rc) return rc;
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = h->use_tc_select ? key_inv_norms(h, t->keys0, t->keys1, s) : normalise_keys(h, t->keys0, t->keys1, s);
+    rc = normalise_keys(h, t->keys0, t->keys1, s);
+    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
     if (rc) return rc;
     const int ab = act_bytes(c.act_dtype);
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
@@ -427,8 +441,8 @@ extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64
     dt.x = h->d_x[0]; dt.out = h->d_out[0];
     rc = check_tensors(h, &dt, true);
     if (rc) return rc;
-    rc = h->use_tc_select ? key_inv_norms(h, t->keys0, t->keys1, h->st_run)
-                          : normalise_keys(h, t->keys0, t->keys1, h->st_run);
+    rc = normalise_keys(h, t->keys0, t->keys1, h->st_run);
+    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, h->st_run);
     if (rc) return rc;
 
     const int ab = act_bytes(c.act_dtype);

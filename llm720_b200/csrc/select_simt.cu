@@ -31,8 +31,15 @@ __global__ void __launch_bounds__(THREADS, 2) select_simt_kernel(SelectArgs a) {
     float* kt = smem + MAXHW * R;     // [hw][KT]  key tile, transposed
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int64_t row0 = static_cast<int64_t>(blockIdx.x) * R;
     const int hw = a.Q / 2;
+    // Either all rows [0, rows), or only the rows named in row_list (the rows another kernel left over).
+    const int64_t nrows = a.row_list ? static_cast<int64_t>(*a.row_count) : a.rows;
+    for (int64_t blk = blockIdx.x; blk * R < nrows; blk += gridDim.x) {
+    const int64_t row0 = blk * R;
+    auto row_of = [&](int64_t i) -> int64_t {       // i-th row of this pass -> row of the layer, or -1
+        if (i >= nrows) return -1;
+        return a.row_list ? static_cast<int64_t>(a.row_list[i]) : i;
+    };
 
     float lv[2][4];
     int li[2][4];
@@ -47,13 +54,23 @@ __global__ void __launch_bounds__(THREADS, 2) select_simt_kernel(SelectArgs a) {
 
         __syncthreads();   // everyone is done with the previous half's qh
         {   // lane = row, warp = 16-wide slice of the half
-            const int64_t r = row0 + lane;
+            const int64_t r = row_of(row0 + lane);
             for (int c0 = warp * 16; c0 < hw; c0 += 8 * 16) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                     const int c = c0 + e;
-                    if (c < hw)
-                        qh[c * R + lane] = (r < a.rows) ? a.q_hat[r * a.Q + half * hw + c] : 0.f;
+                    if (c < hw) {
+                        float qv = 0.f;
+                        if (r >= 0) {
+                            const int64_t o = r * a.Q + half * hw + c;
+                            if (a.q_split)      // hi + mid + lo bf16 terms: the fp32 value exactly
+                                qv = (__bfloat162float(a.q_split[o]) + __bfloat162float(a.q_split[o + a.split_stride])) +
+                                     __bfloat162float(a.q_split[o + 2 * a.split_stride]);
+                            else
+                                qv = a.q_hat[o];
+                        }
+                        qh[c * R + lane] = qv;
+                    }
                 }
             }
         }
@@ -107,8 +124,8 @@ __global__ void __launch_bounds__(THREADS, 2) select_simt_kernel(SelectArgs a) {
     // (a+1)(b+1) <= k can reach the top k because both lists are sorted.
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int64_t r = row0 + warp * 4 + i;
-        if (r >= a.rows) continue;   // warp-uniform
+        const int64_t r = row_of(row0 + warp * 4 + i);
+        if (r < 0) continue;   // warp-uniform
         float fv = -INFINITY;
         int fi = INT_MAX;
         for (int p = 0; p < a.n_pairs; ++p) {
@@ -133,6 +150,7 @@ __global__ void __launch_bounds__(THREADS, 2) select_simt_kernel(SelectArgs a) {
             if (a.raw_scores) a.raw_scores[o] = fv;
         }
     }
+    }
 }
 
 }  // namespace
@@ -144,7 +162,8 @@ cudaError_t select_simt_setup() {
 
 cudaError_t launch_select_simt(const SelectArgs& a, cudaStream_t s) {
     if (a.rows == 0) return cudaSuccess;
-    const unsigned grid = static_cast<unsigned>((a.rows + R - 1) / R);
+    // with a row list the number of rows is only known on the device: a small fixed grid loops over it
+    const unsigned grid = a.row_list ? 296u : static_cast<unsigned>((a.rows + R - 1) / R);
     select_simt_kernel<<<grid, THREADS, SMEM_BYTES, s>>>(a);
     return cudaGetLastError();
 }

@@ -1,32 +1,47 @@
 // Product-key selection on the tensor cores (bf16 layers): the two sub-key
 // score contractions run as tcgen05 MMAs with fp32 accumulators in TMEM, and
 // the per-half top-k, the candidate sums, the final top-k, the softmax and
-// the flat expert ids are computed straight out of TMEM.  No score reaches HBM.
+// the flat expert ids are computed from TMEM with warp-wide votes and
+// reductions.  No score reaches HBM.
 //
 // Follows llm/models/experts.py:153-163 (scores), :168-192 (per-half top-k'),
 // :203-259 (candidate sums, flat ids, final top-k) and :327 (softmax).
 //
 // Exactness.  The reference's fp32 scores are reproduced to fp32 rounding
 // level, not approximated: the normalised query half is fed as three bf16
-// terms (hi + mid + lo carry 24 bits of the fp32 value), the sub-keys of a
+// terms (hi + mid + lo carry the 24 bits of the fp32 value), the sub-keys of a
 // bf16 layer are exactly representable, every bf16 x bf16 product is exact in
 // fp32, and the three partial contractions accumulate in the same fp32 TMEM
-// accumulator.  The key's 1/||k|| is applied per column afterwards.
+// accumulator.  The key's 1/||k|| is applied afterwards.
 //
-// Work split in one CTA (128 (token, head) rows per tile, persistent grid):
-//   warp 0      TMA producer: the query tile of a half (3 terms), then the
-//               key chunks (128 keys) through a ring;
-//   warp 1      MMA issuer: 128x128 accumulators, four in flight in TMEM;
-//   warps 4-7   scan group 0, warps 8-11 scan group 1 (warps 2-3 idle): thread = TMEM lane =
-//               one row; the groups take alternate chunks.  A thread filters
-//               its row's scores against its current 16th-best value, queues
-//               the survivors in shared memory and, when a queue runs full,
-//               the warp inserts the queued (score, key) pairs into
-//               register-resident sorted lists; this keeps the expensive
-//               insertion off the per-element path.
-// Ordering among exactly equal scores: smaller sub-key index first (per
-// half), smaller candidate position first (final), as in select_simt.cu.
+// Layout of the work.  One CTA owns a tile of 128 (token, head) rows at a time
+// (persistent grid).  The accumulator is KEY-major: M = 128 sub-keys (one chunk
+// of the table), N = the 128 rows, so a TMEM lane is a key and a thread that
+// reads 32 columns holds the scores of 32 rows for its key.  A question about
+// one row and 32 keys ("largest score?", "which keys reach the row's bound?")
+// is then ONE warp-wide reduction or vote, with the same control flow in every
+// lane: no lane-dependent branches, no queues, no load imbalance.
+//
+// Per tile and query half, two passes over the sub-key table (the tensor cores
+// recompute the scores for the second pass; they are otherwise idle):
+//   pass 0  per row, the largest score of every group of 32 keys (redux.max)
+//           -> shared memory; the 16th largest group maximum of a row is a
+//           lower bound of its 16th best score (16 distinct scores reach it)
+//           and typically only about 22 scores of a 1024-key table do;
+//   pass 1  per row and group, a vote "score >= bound"; the few hits are
+//           appended to the row's candidate list in shared memory;
+//   then    one warp per row extracts the 16 best candidates in order.
+// After both halves: candidate sums (a+1)(b+1) <= k, final top-k, softmax, ids,
+// again one warp per row.  Rows whose candidate list overflowed (heavily
+// clustered scores) are written to a list that the exact CUDA-core kernel
+// reprocesses (select_simt.cu), so the result never depends on the heuristic.
+//
+// Warps: 0 = TMA producer, 1 = MMA issuer, 2-3 idle, 4-19 = 16 scan warps
+// (scan warp s reads TMEM lanes 32*(s&3).. and columns 32*(s>>2)..).
+// Ordering among exactly equal scores: smaller sub-key index first (per half),
+// smaller candidate position first (final), as in select_simt.cu.
 #include <float.h>
+#include <limits.h>
 
 #include "kernels.h"
 #include "tc_common.cuh"
@@ -35,28 +50,40 @@ namespace peer {
 
 namespace {
 
-constexpr int BM = 128;            // rows per tile
-constexpr int NC = 128;            // keys per chunk (UMMA N)
+constexpr int BM = 128;            // rows per tile (MMA N)
+constexpr int NC = 128;            // keys per chunk (MMA M)
 constexpr int BOX_BYTES = 128 * 64 * 2;   // one TMA box: 128 rows x 64 bf16
 constexpr int MAX_KA = 2;          // 64-column boxes per half (half width 64 or 128)
-constexpr int A_BYTES = 3 * MAX_KA * BOX_BYTES;     // 96 KB
-constexpr int B_STAGE_BYTES = MAX_KA * BOX_BYTES;   // 32 KB
-constexpr int B_STAGES = 2;
+constexpr int Q_BYTES = 3 * MAX_KA * BOX_BYTES;     // 96 KB: query tile, three terms
+constexpr int K_STAGE_BYTES = MAX_KA * BOX_BYTES;   // 32 KB: one key chunk
+constexpr int K_STAGES = 2;
 constexpr int N_ACC = 4;
-constexpr int QC = 32;             // queue entries per row and scan group
-constexpr int LK = 16;             // list length kept per half
-constexpr int THREADS = 384;       // warps 0-3: TMA, MMA, two idle; warps 4-7 and 8-11: the scan groups
-constexpr int CTRL_REGS = 40, SCAN_REGS = 232;   // 128*40 + 256*232 = 384*168 registers
+constexpr int MAX_GROUPS = 32;     // key groups per row and half whose maxima bound the 16th best score
+constexpr int CAP = 32;            // candidates per row and half
+constexpr int LK = 16;             // list length per half (top_k and k' <= 16)
+constexpr int SCAN_WARPS = 16;
+constexpr int POOL = 256;          // candidates beyond CAP, all rows of the tile together
+constexpr int LOST = 1 << 20;      // added to a row's count when one of its candidates could not be kept
+constexpr int STAGE_CAP = 8;       // scores a lane can hold back per chunk before they go to the row lists
+constexpr int THREADS = 128 + SCAN_WARPS * 32;
+constexpr int CTRL_REGS = 24, SCAN_REGS = 112;     // 128*24 + 512*112 <= 640*96 registers at launch
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int KEY_MIN = INT_MIN;   // ordered-int image of "no score"
 
 struct Smem {
-    static constexpr size_t a_off = 0;
-    static constexpr size_t b_off = a_off + A_BYTES;
-    static constexpr size_t q_off = b_off + static_cast<size_t>(B_STAGES) * B_STAGE_BYTES;   // [2][QC][128] x 8 B
-    static constexpr size_t tau_off = q_off + 2 * QC * BM * 8;                                 // [2][128] floats
-    static constexpr size_t bar_off = tau_off + 2 * BM * sizeof(float);
+    static constexpr size_t q_off = 0;
+    static constexpr size_t k_off = q_off + Q_BYTES;
+    static constexpr size_t gmax_off = k_off + static_cast<size_t>(K_STAGES) * K_STAGE_BYTES;   // [MAX_GROUPS][128] int
+    static constexpr size_t cand_off = gmax_off + MAX_GROUPS * BM * 4;                           // [128][CAP] (key, col)
+    static constexpr size_t cnt_off = cand_off + BM * CAP * 8;                                   // [128] int
+    static constexpr size_t tau_off = cnt_off + BM * 4;                                          // [128] int
+    static constexpr size_t stage_off = gmax_off;          // [STAGE_CAP][512] float: pass 1 only, when the group maxima are dead
+    static constexpr size_t pool_off = tau_off + BM * 4;                                         // [POOL] (row, score, sub-key, -)
+    static constexpr size_t bar_off = pool_off + POOL * 16;
     static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 16 + 1008;
 };
+static_assert(Smem::total <= 227 * 1024, "shared memory budget");
+static_assert(STAGE_CAP * SCAN_WARPS * 32 * 4 <= MAX_GROUPS * BM * 4, "the staging slots reuse the group maxima");
 
 struct SelTcParams {
     const float* invn0; const float* invn1;   // 1/||key|| per sub-key (or 1)
@@ -65,43 +92,16 @@ struct SelTcParams {
     int Q, n0, n1, kp0, kp1, k, mult0, mult1;
     int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores;
     int* status;
+    int32_t* overflow_rows; int* overflow_count;   // rows left to the exact kernel
 };
 
-// Sorted-list insertion, written as a pure function of the OLD list (new arrays, then copy):
-// an in-place form of the same logic with a precomputed bool array was observed to be
-// miscompiled by nvcc 12.9 for sm_100a (the first inserted element appeared twice).
-// Values move through min/max; the indices follow the same predicates.
-// strict: an equal score stays behind the entries already present.
-__device__ __forceinline__ void insert_pair(float (&v)[LK], int (&c)[LK], float x, int col) {
-    int nc[LK];
-#pragma unroll
-    for (int i = 0; i < LK; ++i) {
-        const bool pi = x > v[i];
-        const bool pm = (i == 0) ? false : (x > v[i == 0 ? 0 : i - 1]);
-        nc[i] = pi ? (pm ? c[i == 0 ? 0 : i - 1] : col) : c[i];
-    }
-#pragma unroll
-    for (int i = LK - 1; i >= 1; --i) v[i] = fmaxf(v[i], fminf(v[i - 1], x));
-    v[0] = fmaxf(v[0], x);
-#pragma unroll
-    for (int i = 0; i < LK; ++i) c[i] = nc[i];
-}
-// full order: score descending, then index ascending
-__device__ __forceinline__ void insert_pair_ordered(float (&v)[LK], int (&c)[LK], float x, int col) {
-    int nc[LK];
-#pragma unroll
-    for (int i = 0; i < LK; ++i) {
-        const int j = i == 0 ? 0 : i - 1;
-        const bool pi = (x > v[i]) || (x == v[i] && col < c[i]);
-        const bool pm = (i == 0) ? false : ((x > v[j]) || (x == v[j] && col < c[j]));
-        nc[i] = pi ? (pm ? c[j] : col) : c[i];
-    }
-#pragma unroll
-    for (int i = LK - 1; i >= 1; --i) v[i] = fmaxf(v[i], fminf(v[i - 1], x));
-    v[0] = fmaxf(v[0], x);
-#pragma unroll
-    for (int i = 0; i < LK; ++i) c[i] = nc[i];
-}
+// order-preserving map fp32 -> int32 (and back): integer compares and redux.max work on scores
+__device__ __forceinline__ int f2key(float x) { const int i = __float_as_int(x); return i ^ ((i >> 31) & 0x7fffffff); }
+__device__ __forceinline__ float key2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+
+// candidate pairs of the final combine, two per lane: (a, b) with (a+1)(b+1) <= 16, row-major order
+__constant__ unsigned char c_pair_a[64];
+__constant__ unsigned char c_pair_b[64];
 
 __global__ void __launch_bounds__(THREADS, 1)
 select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k0,
@@ -109,25 +109,30 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float* s_gmax = reinterpret_cast<float*>(smem + Smem::gmax_off); // [group][row]
+    int2* s_cand = reinterpret_cast<int2*>(smem + Smem::cand_off);   // [row][CAP] (score key, sub-key index)
+    int* s_cnt = reinterpret_cast<int*>(smem + Smem::cnt_off);
+    float* s_tau = reinterpret_cast<float*>(smem + Smem::tau_off);
+    float* s_stage = reinterpret_cast<float*>(smem + Smem::stage_off);
+    int4* s_pool = reinterpret_cast<int4*>(smem + Smem::pool_off);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::bar_off);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
-    const uint32_t sA = smem_u32(smem + Smem::a_off), sB = smem_u32(smem + Smem::b_off);
+    int* s_pool_cnt = reinterpret_cast<int*>(tmem_slot + 1);
+    const uint32_t sQ = smem_u32(smem + Smem::q_off), sK = smem_u32(smem + Smem::k_off);
     const uint32_t bar0 = smem_u32(bars);
-    const uint32_t a_full = bar0, a_empty = bar0 + 8;
-    auto b_full = [&](int s) { return bar0 + 8u * (2 + s); };
-    auto b_empty = [&](int s) { return bar0 + 8u * (2 + B_STAGES + s); };
-    auto acc_full = [&](int a) { return bar0 + 8u * (2 + 2 * B_STAGES + a); };
-    auto acc_empty = [&](int a) { return bar0 + 8u * (2 + 2 * B_STAGES + N_ACC + a); };
+    const uint32_t q_full = bar0, q_empty = bar0 + 8;
+    auto k_full = [&](int s) { return bar0 + 8u * (2 + s); };
+    auto k_empty = [&](int s) { return bar0 + 8u * (2 + K_STAGES + s); };
+    auto acc_full = [&](int a) { return bar0 + 8u * (2 + 2 * K_STAGES + a); };
+    auto acc_empty = [&](int a) { return bar0 + 8u * (2 + 2 * K_STAGES + N_ACC + a); };
 
     if (tid == 0) {
-        mbar_init(a_full, 1); mbar_init(a_empty, 1);
-        for (int s = 0; s < B_STAGES; ++s) { mbar_init(b_full(s), 1); mbar_init(b_empty(s), 1); }
-        for (int a = 0; a < N_ACC; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 128); }
+        mbar_init(q_full, 1); mbar_init(q_empty, 1);
+        for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
+        for (int a = 0; a < N_ACC; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), SCAN_WARPS * 32); }
         mbar_fence_init();
         tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k0); tc::tma_prefetch_desc(&map_k1);
     }
-    float* tau_sh = reinterpret_cast<float*>(smem + Smem::tau_off);   // each group's current 16th-best score per row
-    if (tid < 2 * BM) tau_sh[tid] = -INFINITY;
     if (warp == 0) {
         __syncwarp();
         tc::tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
@@ -141,213 +146,295 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int KA = hw / 64;                                   // 64-column boxes per half
     const int nch0 = (p.n0 + NC - 1) / NC, nch1 = (p.n1 + NC - 1) / NC;
     const int64_t n_tiles = (p.rows + BM - 1) / BM;
-    const uint32_t a_bytes = 3u * KA * BOX_BYTES, b_bytes = static_cast<uint32_t>(KA) * BOX_BYTES;
+    const uint32_t q_bytes = 3u * KA * BOX_BYTES, k_bytes = static_cast<uint32_t>(KA) * BOX_BYTES;
 
-    // The control warps need few registers; the rest of the launch allocation goes to the scan groups.
+    // The control warps need few registers; the rest of the launch allocation goes to the scan warps.
     if (warp < 4) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CTRL_REGS));
       if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            uint32_t a_phase = 0; int stage = 0; uint32_t b_phase = 0; bool ok = true;
+            uint32_t q_phase = 0; int stage = 0; uint32_t k_phase = 0; bool ok = true;
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (int hf = 0; hf < 2 && ok; ++hf) {
-                    if (!mbar_wait(a_empty, a_phase ^ 1, p.status)) { ok = false; break; }
-                    a_phase ^= 1;
-                    mbar_expect_tx(a_full, a_bytes);
+                    if (!mbar_wait(q_empty, q_phase ^ 1, p.status)) { ok = false; break; }
+                    q_phase ^= 1;
+                    mbar_expect_tx(q_full, q_bytes);
                     for (int t = 0; t < 3; ++t)
                         for (int ka = 0; ka < KA; ++ka)
-                            tc::tma_load_2d(sA + (t * KA + ka) * BOX_BYTES, &map_q, hf * hw + ka * 64,
-                                            static_cast<int>(t * p.term_rows + tile * BM), a_full);
+                            tc::tma_load_2d(sQ + (t * KA + ka) * BOX_BYTES, &map_q, hf * hw + ka * 64,
+                                            static_cast<int>(t * p.term_rows + tile * BM), q_full);
                     const int nch = hf ? nch1 : nch0;
                     const CUtensorMap* mk = hf ? &map_k1 : &map_k0;
-                    for (int c = 0; c < nch; ++c) {
-                        if (!mbar_wait(b_empty(stage), b_phase ^ 1, p.status)) { ok = false; break; }
-                        mbar_expect_tx(b_full(stage), b_bytes);
+                    for (int c2 = 0; c2 < 2 * nch; ++c2) {          // two passes over the sub-keys
+                        const int c = c2 < nch ? c2 : c2 - nch;
+                        if (!mbar_wait(k_empty(stage), k_phase ^ 1, p.status)) { ok = false; break; }
+                        mbar_expect_tx(k_full(stage), k_bytes);
                         for (int ka = 0; ka < KA; ++ka)
-                            tc::tma_load_2d(sB + stage * B_STAGE_BYTES + ka * BOX_BYTES, mk, ka * 64, c * NC, b_full(stage));
-                        if (++stage == B_STAGES) { stage = 0; b_phase ^= 1; }
+                            tc::tma_load_2d(sK + stage * K_STAGE_BYTES + ka * BOX_BYTES, mk, ka * 64, c * NC, k_full(stage));
+                        if (++stage == K_STAGES) { stage = 0; k_phase ^= 1; }
                     }
                 }
             }
         }
       } else if (warp == 1) {
-        // ---------------- MMA issuer ----------------
+        // ---------------- MMA issuer: D[key, row] = sum over the three query terms of K . q^T ----------------
         if (lane == 0) {
-            const uint32_t idesc = tc::idesc_bf16_f32(BM, NC);
-            uint32_t a_phase = 0; int stage = 0; uint32_t b_phase = 0; uint32_t g = 0; bool ok = true;
+            const uint32_t idesc = tc::idesc_bf16_f32(NC, BM);
+            uint32_t q_phase = 0; int stage = 0; uint32_t k_phase = 0; uint32_t g = 0; bool ok = true;
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (int hf = 0; hf < 2 && ok; ++hf) {
-                    if (!mbar_wait(a_full, a_phase, p.status)) { ok = false; break; }
-                    a_phase ^= 1;
+                    if (!mbar_wait(q_full, q_phase, p.status)) { ok = false; break; }
+                    q_phase ^= 1;
                     const int nch = hf ? nch1 : nch0;
-                    for (int c = 0; c < nch; ++c, ++g) {
+                    for (int c = 0; c < 2 * nch; ++c, ++g) {
                         const int acc = g & (N_ACC - 1);
                         if (!mbar_wait(acc_empty(acc), ((g / N_ACC) & 1) ^ 1, p.status)) { ok = false; break; }
-                        if (!mbar_wait(b_full(stage), b_phase, p.status)) { ok = false; break; }
+                        if (!mbar_wait(k_full(stage), k_phase, p.status)) { ok = false; break; }
                         tc::fence_after_sync();
-                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * NC;
+                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * BM;
                         uint32_t first = 0;
                         for (int t = 0; t < 3; ++t)
                             for (int ka = 0; ka < KA; ++ka) {
-                                const uint64_t ad = tc::smem_desc_sw128(sA + (t * KA + ka) * BOX_BYTES);
-                                const uint64_t bd = tc::smem_desc_sw128(sB + stage * B_STAGE_BYTES + ka * BOX_BYTES);
+                                const uint64_t kd = tc::smem_desc_sw128(sK + stage * K_STAGE_BYTES + ka * BOX_BYTES);
+                                const uint64_t qd = tc::smem_desc_sw128(sQ + (t * KA + ka) * BOX_BYTES);
 #pragma unroll
                                 for (int k = 0; k < 4; ++k) {
-                                    tc::umma_bf16(d_tmem, ad + 2 * k, bd + 2 * k, idesc, first);
+                                    tc::umma_bf16(d_tmem, kd + 2 * k, qd + 2 * k, idesc, first);
                                     first = 1;
                                 }
                             }
-                        tc::umma_commit(b_empty(stage));
+                        tc::umma_commit(k_empty(stage));
                         tc::umma_commit(acc_full(acc));
-                        if (++stage == B_STAGES) { stage = 0; b_phase ^= 1; }
+                        if (++stage == K_STAGES) { stage = 0; k_phase ^= 1; }
                     }
-                    if (ok) tc::umma_commit(a_empty);     // the query tile of this half is no longer read
+                    if (ok) tc::umma_commit(q_empty);     // the query tile of this half is no longer read
                 }
             }
         }
       }
     } else {
+        // ---------------- scan warps ----------------
         asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SCAN_REGS));
-        // ---------------- scan groups ----------------
-        const int wg = (warp - 4) >> 2;               // 0 or 1
-        const int quarter = warp & 3;
-        const int row = quarter * 32 + lane;
-        uint2* queue = reinterpret_cast<uint2*>(smem + Smem::q_off) + static_cast<size_t>(wg) * QC * BM;   // [QC][128]
-        uint2* other_queue = reinterpret_cast<uint2*>(smem + Smem::q_off) + static_cast<size_t>(wg ^ 1) * QC * BM;
-        uint32_t g = 0;                                // global chunk counter (all chunks, both groups)
+        const int s = warp - 4;                        // 0..15
+        const int quarter = warp & 3;                  // TMEM lanes (keys) 32*quarter..
+        const int cg = s >> 2;                         // TMEM columns (rows) 32*cg..
+        const int half16 = lane & 16;                  // rows 4..7 of a warp keep their lists in lanes 16..31
+        uint32_t g = 0;
         bool ok = true;
-        int64_t tile_iter = 0;
-        for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tile_iter) {
-            const bool merger = (tile_iter & 1) == wg;
-            float hv[2][LK]; int hc[2][LK];           // merged per-half lists (merger group only)
+        for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+            // sorted lists of my 8 rows, per half: rows 0-3 in lanes 0-15, rows 4-7 in lanes 16-31
+            float hv[2][4]; int hc[2][4];
+            unsigned overflow = 0;                     // bit rr: row 8s+rr overflowed its candidate list
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
                 const int n = hf ? p.n1 : p.n0;
                 const int nch = hf ? nch1 : nch0;
                 const float* __restrict__ invn = hf ? p.invn1 : p.invn0;
-                float v[LK]; int c[LK];
-#pragma unroll
-                for (int i = 0; i < LK; ++i) { v[i] = -INFINITY; c[i] = 0x7fffffff; }
-                int cnt = 0;
-                float tau = -INFINITY;
-                // A score below the OTHER group's 16th-best cannot be among the row's 16 best either,
-                // so the two groups share their thresholds through shared memory.
-                volatile float* tau_mine = tau_sh + wg * BM + row;
-                volatile float* tau_other = tau_sh + (wg ^ 1) * BM + row;
-                auto drain = [&]() {
-                    const int maxc = __reduce_max_sync(FULL_MASK, cnt);
-                    for (int i = 0; i < maxc; ++i) {
-                        float x = -INFINITY; int col = 0;
-                        if (i < cnt) { const uint2 e = queue[i * BM + row]; x = __uint_as_float(e.x); col = static_cast<int>(e.y); }
-                        if (!__any_sync(FULL_MASK, x > v[LK - 1])) continue;
-                        insert_pair(v, c, x, col);
-                    }
-                    cnt = 0;
-                    *tau_mine = v[LK - 1];
-                    tau = fmaxf(v[LK - 1], *tau_other);
-                };
-                for (int ch = 0; ch < nch; ++ch, ++g) {
-                    if ((g & 1u) != static_cast<uint32_t>(wg)) continue;
-                    const int acc = g & (N_ACC - 1);
-                    if (ok && !mbar_wait(acc_full(acc), (g / N_ACC) & 1, p.status)) ok = false;
-                    if (!ok) continue;
-                    tc::fence_after_sync();
-                    tau = fmaxf(tau, *tau_other);
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * NC;
-                    const int col0 = ch * NC;
 #pragma unroll 1
-                    for (int b = 0; b < NC / 32; ++b) {
+                for (int pass = 0; pass < 2; ++pass) {
+                    // pass 0: bnd[j] = largest score of my keys (one per chunk) for row j;
+                    // pass 1: bnd[j] = the bound of row j
+                    float bnd[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) bnd[j] = pass ? s_tau[cg * 32 + j] : -INFINITY;
+                    for (int ch = 0; ch < nch; ++ch, ++g) {
+                        const int acc = g & (N_ACC - 1);
+                        if (ok && !mbar_wait(acc_full(acc), (g / N_ACC) & 1, p.status)) ok = false;
+                        if (!ok) continue;
+                        tc::fence_after_sync();
                         uint32_t r[32];
-                        tc::tmem_ld32(taddr + b * 32, r);
+                        tc::tmem_ld32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * BM + cg * 32, r);
+                        const int key = ch * NC + quarter * 32 + lane;       // this lane's sub-key
+                        // keys past the end of the table get a NaN scale: their scores lose every comparison
+                        const float sc = key < n ? __ldg(invn + key) : __int_as_float(0x7fc00000);
                         tc::tmem_ld_wait();
-                        if (b == NC / 32 - 1) {        // accumulator fully read: hand it back to the MMA warp
-                            tc::fence_before_sync();
-                            mbar_arrive(acc_empty(acc));
-                        }
-                        const int cb = col0 + b * 32;
-                        if (cb >= n) continue;
-                        if (cb + 32 <= n) {
+                        tc::fence_before_sync();
+                        mbar_arrive(acc_empty(acc));                         // scores are in registers
+                        if (pass == 0) {
 #pragma unroll
-                            for (int j8 = 0; j8 < 32; j8 += 8) {
-                                const float4 s0 = __ldg(reinterpret_cast<const float4*>(invn + cb + j8));
-                                const float4 s1 = __ldg(reinterpret_cast<const float4*>(invn + cb + j8 + 4));
-                                const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                            for (int j = 0; j < 32; ++j) bnd[j] = fmaxf(bnd[j], __uint_as_float(r[j]) * sc);
+                        } else {
+                            // Every lane notes its own hits (score into a private slot, row into a bit
+                            // mask) without votes or branches, then the lanes append their hits to the
+                            // rows' lists side by side.
+                            float* slot = s_stage + (s * 32 + lane);
+                            unsigned myhits = 0; int nh = 0;
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    // branch-free push: always store into the next free slot, keep it only if it passes
-                                    const float x = __uint_as_float(r[j8 + e]) * sc[e];
-                                    queue[cnt * BM + row] = make_uint2(__float_as_uint(x), static_cast<uint32_t>(cb + j8 + e));
-                                    cnt += (x > tau) ? 1 : 0;
-                                }
-                                if (__any_sync(FULL_MASK, cnt > QC - 8)) drain();
+                            for (int j = 0; j < 32; ++j) {
+                                const float x = __uint_as_float(r[j]) * sc;
+                                const bool hit = x >= bnd[j];
+                                if (hit) slot[min(nh, STAGE_CAP - 1) * (SCAN_WARPS * 32)] = x;
+                                nh += hit ? 1 : 0;
+                                myhits |= hit ? (1u << j) : 0u;
                             }
-                        } else {                       // ragged last batch of the table
-#pragma unroll
-                            for (int j8 = 0; j8 < 32; j8 += 8) {
-#pragma unroll
-                                for (int e = 0; e < 8; ++e) {
-                                    const int col = cb + j8 + e;
-                                    const float x = (col < n) ? __uint_as_float(r[j8 + e]) * __ldg(invn + col) : -INFINITY;
-                                    queue[cnt * BM + row] = make_uint2(__float_as_uint(x), static_cast<uint32_t>(col));
-                                    cnt += (x > tau) ? 1 : 0;
+                            int taken = 0;
+                            while (__any_sync(FULL_MASK, myhits != 0)) {
+                                if (myhits) {
+                                    const int row = cg * 32 + __ffs(myhits) - 1;
+                                    myhits &= myhits - 1;
+                                    if (taken < STAGE_CAP - 1 || nh <= STAGE_CAP) {
+                                        const float x = slot[taken * (SCAN_WARPS * 32)];
+                                        const int pos = atomicAdd(&s_cnt[row], 1);
+                                        if (pos < CAP) {
+                                            s_cand[row * CAP + pos] = make_int2(__float_as_int(x), key);
+                                        } else {                             // a long list continues in the tile's pool
+                                            const int pp = atomicAdd(s_pool_cnt, 1);
+                                            if (pp < POOL) s_pool[pp] = make_int4(row, __float_as_int(x), key, 0);
+                                            else atomicAdd(&s_cnt[row], LOST);
+                                        }
+                                    } else {
+                                        atomicAdd(&s_cnt[row], LOST);        // slot lost: the row goes to the exact kernel
+                                    }
+                                    ++taken;
                                 }
-                                if (__any_sync(FULL_MASK, cnt > QC - 8)) drain();
                             }
                         }
                     }
+                    if (pass == 0) {
+                        // group maxima: 4 adjacent lanes x all chunks = one group; 8 groups per warp, 32 per row
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float m = fmaxf(bnd[j], __shfl_xor_sync(FULL_MASK, bnd[j], 1));
+                            m = fmaxf(m, __shfl_xor_sync(FULL_MASK, m, 2));
+                            if ((lane & 3) == 0) s_gmax[(quarter * 8 + (lane >> 2)) * BM + cg * 32 + j] = m;
+                        }
+                    }
+                    asm volatile("bar.sync 1, 512;" ::: "memory");
+                    if (pass == 0) {
+                        // bound of my 8 rows: the 16th largest of the row's 32 group maxima (16 distinct scores reach it)
+                        // (the 8 rows' sorting networks are written side by side so their shuffles overlap)
+                        float tv[8];
+#pragma unroll
+                        for (int rr = 0; rr < 8; ++rr) tv[rr] = s_gmax[lane * BM + s * 8 + rr];
+#pragma unroll
+                        for (int k = 2; k <= 32; k <<= 1)
+#pragma unroll
+                            for (int j = k >> 1; j > 0; j >>= 1) {
+                                const bool keep_max = ((lane & j) == 0) == ((lane & k) == 0 || k == 32);
+#pragma unroll
+                                for (int rr = 0; rr < 8; ++rr) {
+                                    const float o = __shfl_xor_sync(FULL_MASK, tv[rr], j);
+                                    tv[rr] = keep_max ? fmaxf(tv[rr], o) : fminf(tv[rr], o);
+                                }
+                            }
+#pragma unroll
+                        for (int rr = 0; rr < 8; ++rr) {
+                            const float t = __shfl_sync(FULL_MASK, tv[rr], LK - 1);
+                            if (lane == 0) { s_tau[s * 8 + rr] = t; s_cnt[s * 8 + rr] = 0; }
+                        }
+                        if (s == 0 && lane == 0) *s_pool_cnt = 0;
+                        asm volatile("bar.sync 1, 512;" ::: "memory");
+                    }
                 }
-                drain();
-                // ---- merge the two groups' lists of this half (both groups take part in both barriers)
-                if (!merger) {
+                // the 16 best candidates of my 8 rows, in order (score descending, sub-key ascending)
 #pragma unroll
-                    for (int i = 0; i < LK; ++i)
-                        queue[i * BM + row] = make_uint2(__float_as_uint(v[i]), static_cast<uint32_t>(c[i]));
-                }
-                asm volatile("bar.sync 2, 256;" ::: "memory");
-                *tau_mine = -INFINITY;                 // both groups are done scanning this half
-                uint2 oth[LK];
-                if (merger) {
+                for (int rb = 0; rb < 8; rb += 4) {          // four rows' networks side by side
+                    float v[4]; int c[4];
+                    unsigned pooled = 0;                     // bit q: the row's list continues in the pool
 #pragma unroll
-                    for (int i = 0; i < LK; ++i) oth[i] = other_queue[i * BM + row];
-                }
-                asm volatile("bar.sync 3, 256;" ::: "memory");
-                if (merger) {
+                    for (int q = 0; q < 4; ++q) {
+                        const int row = s * 8 + rb + q;
+                        const int cnt = s_cnt[row];
+                        if (cnt >= LOST) overflow |= 1u << (rb + q);
+                        else if (cnt > CAP) pooled |= 1u << q;
+                        v[q] = -INFINITY; c[q] = INT_MAX;
+                        if (lane < min(cnt, CAP)) { const int2 e = s_cand[row * CAP + lane]; v[q] = __int_as_float(e.x); c[q] = e.y; }
+                    }
 #pragma unroll
-                    for (int i = 0; i < LK; ++i)
-                        insert_pair_ordered(v, c, __uint_as_float(oth[i].x), static_cast<int>(oth[i].y));
+                    for (int k = 2; k <= 32; k <<= 1)
 #pragma unroll
-                    for (int i = 0; i < LK; ++i) { hv[hf][i] = v[i]; hc[hf][i] = c[i]; }
+                        for (int j = k >> 1; j > 0; j >>= 1) {
+                            const bool keep_first = ((lane & j) == 0) == ((lane & k) == 0 || k == 32);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float ov = __shfl_xor_sync(FULL_MASK, v[q], j);
+                                const int oc = __shfl_xor_sync(FULL_MASK, c[q], j);
+                                const bool mine_first = (v[q] > ov) || (v[q] == ov && c[q] < oc);
+                                const bool keep_mine = mine_first == keep_first;
+                                v[q] = keep_mine ? v[q] : ov;
+                                c[q] = keep_mine ? c[q] : oc;
+                            }
+                        }
+                    if (pooled) {                            // rare: insert the pool's entries of these rows
+                        const int np = min(*s_pool_cnt, POOL);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            if (!(pooled & (1u << q))) continue;
+                            for (int e = 0; e < np; ++e) {
+                                const int4 pe = s_pool[e];
+                                if (pe.x != s * 8 + rb + q) continue;
+                                const float ex = __int_as_float(pe.y);
+                                const bool before = (v[q] > ex) || (v[q] == ex && c[q] < pe.z);
+                                const int at = __popc(__ballot_sync(FULL_MASK, before));
+                                const float uv = __shfl_up_sync(FULL_MASK, v[q], 1);
+                                const int uc = __shfl_up_sync(FULL_MASK, c[q], 1);
+                                if (lane == at) { v[q] = ex; c[q] = pe.z; }
+                                else if (lane > at) { v[q] = uv; c[q] = uc; }
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        if (rb) {                            // move lanes 0..15 to lanes 16..31
+                            v[q] = __shfl_sync(FULL_MASK, v[q], lane & 15);
+                            c[q] = __shfl_sync(FULL_MASK, c[q], lane & 15);
+                        }
+                        if ((rb != 0) == (half16 != 0)) { hv[hf][q] = v[q]; hc[hf][q] = c[q]; }
+                    }
                 }
             }
-            if (!merger || !ok) continue;
-            // ---- candidate sums, final top-k, softmax, ids (thread = row)
-            const int64_t grow = tile * BM + row;
-            float fv[LK]; int fid[LK];
+            if (!ok) continue;
+            // ---- candidate sums, final top-k, softmax, ids: one warp per row
+            const int pa0 = c_pair_a[lane], pb0 = c_pair_b[lane], pa1 = c_pair_a[lane + 32], pb1 = c_pair_b[lane + 32];
+            // only pairs with (a+1)(b+1) <= k can reach the top k: both lists are sorted
+            const bool use0 = pa0 < p.kp0 && pb0 < p.kp1 && (pa0 + 1) * (pb0 + 1) <= p.k;
+            const bool use1 = pa1 < p.kp0 && pb1 < p.kp1 && (pa1 + 1) * (pb1 + 1) <= p.k;
 #pragma unroll
-            for (int i = 0; i < LK; ++i) { fv[i] = -INFINITY; fid[i] = 0; }
+            for (int rb = 0; rb < 8; rb += 4) {              // four rows side by side
+                const int base = rb ? 16 : 0;                  // lane base + j: j-th best of each half
+                const int pos0 = pa0 * 16 + pb0, pos1 = pa1 * 16 + pb1;
+                int k0[4], k1[4], fk[4], fpos[4];
+                bool act[4];
 #pragma unroll
-            for (int a = 0; a < LK; ++a) {
-#pragma unroll
-                for (int b = 0; b < LK / (a + 1); ++b) {
-                    // only pairs with (a+1)(b+1) <= k can reach the top k: both lists are sorted
-                    if ((a + 1) * (b + 1) <= p.k && a < p.kp0 && b < p.kp1)
-                        insert_pair(fv, fid, hv[0][a] + hv[1][b], hc[0][a] * p.mult0 + hc[1][b] * p.mult1);
+                for (int q = 0; q < 4; ++q) {
+                    const int64_t grow = tile * BM + s * 8 + rb + q;
+                    act[q] = grow < p.rows && !(overflow & (1u << (rb + q)));    // warp-uniform
+                    if (grow < p.rows && (overflow & (1u << (rb + q))) && lane == 0)   // left to the exact kernel
+                        p.overflow_rows[atomicAdd(p.overflow_count, 1)] = static_cast<int32_t>(grow);
+                    const float s0 = hv[0][q], s1 = hv[1][q];
+                    const float v0 = __shfl_sync(FULL_MASK, s0, base + (pa0 & 15)) + __shfl_sync(FULL_MASK, s1, base + (pb0 & 15));
+                    const float v1 = __shfl_sync(FULL_MASK, s0, base + (pa1 & 15)) + __shfl_sync(FULL_MASK, s1, base + (pb1 & 15));
+                    k0[q] = use0 ? f2key(v0) : KEY_MIN; k1[q] = use1 ? f2key(v1) : KEY_MIN;
+                    fk[q] = KEY_MIN; fpos[q] = 0;
                 }
-            }
-            if (grow < p.rows) {
-                float e[LK], sum = 0.f;
+                for (int it = 0; it < p.k; ++it) {
 #pragma unroll
-                for (int i = 0; i < LK; ++i) { e[i] = (i < p.k) ? expf(fv[i] - fv[0]) : 0.f; sum += e[i]; }
-                const float inv = 1.0f / sum;
-                const int64_t o = grow * p.k;
+                    for (int q = 0; q < 4; ++q) {
+                        const int m = __reduce_max_sync(FULL_MASK, max(k0[q], k1[q]));
+                        const int mypos = min(k0[q] == m ? pos0 : INT_MAX, k1[q] == m ? pos1 : INT_MAX);
+                        const int pos = __reduce_min_sync(FULL_MASK, mypos);      // ties: smallest candidate position
+                        if (lane == it) { fk[q] = m; fpos[q] = pos; }
+                        if (k0[q] == m && pos0 == pos) k0[q] = KEY_MIN;
+                        else if (k1[q] == m && pos1 == pos) k1[q] = KEY_MIN;
+                    }
+                }
+                const bool live = lane < p.k;
 #pragma unroll
-                for (int i = 0; i < LK; ++i) {
-                    if (i < p.k) {
-                        if (p.ids32) p.ids32[o + i] = fid[i];
-                        if (p.weights) p.weights[o + i] = e[i] * inv;
-                        if (p.ids64) p.ids64[o + i] = fid[i];
-                        if (p.raw_scores) p.raw_scores[o + i] = fv[i];
+                for (int q = 0; q < 4; ++q) {
+                    const int i0 = __shfl_sync(FULL_MASK, hc[0][q], base + (live ? (fpos[q] >> 4) : 0));
+                    const int i1 = __shfl_sync(FULL_MASK, hc[1][q], base + (live ? (fpos[q] & 15) : 0));
+                    const int id = i0 * p.mult0 + i1 * p.mult1;
+                    const float fv = key2f(fk[q]);
+                    const float top = __shfl_sync(FULL_MASK, fv, 0);
+                    const float e = live ? expf(fv - top) : 0.f;
+                    const float w = e / warp_sum(e);
+                    if (live && act[q]) {
+                        const int64_t o = (tile * BM + s * 8 + rb + q) * p.k + lane;
+                        if (p.ids32) p.ids32[o] = id;
+                        if (p.weights) p.weights[o] = w;
+                        if (p.ids64) p.ids64[o] = id;
+                        if (p.raw_scores) p.raw_scores[o] = fv;
                     }
                 }
             }
@@ -375,11 +462,21 @@ __global__ void key_inv_norm_kernel(const __nv_bfloat16* __restrict__ keys, int 
 }  // namespace
 
 bool select_tc_supported(int act_dtype, int Q, int n0, int n1, int k, int kp0, int kp1) {
+    // lists of at most 16 per half; at least one full chunk of keys per table
     return act_dtype == PEER_DTYPE_BF16 && (Q == 128 || Q == 256) && k <= LK && kp0 <= LK && kp1 <= LK &&
-           n0 % 4 == 0 && n1 % 4 == 0;
+           n0 >= 128 && n1 >= 128;
 }
 
 cudaError_t select_tc_setup() {
+    unsigned char pa[64], pb[64];
+    int np = 0;
+    for (int a = 0; a < LK; ++a)
+        for (int b = 0; b < LK; ++b)
+            if ((a + 1) * (b + 1) <= LK) { pa[np] = static_cast<unsigned char>(a); pb[np] = static_cast<unsigned char>(b); ++np; }
+    for (; np < 64; ++np) { pa[np] = 255; pb[np] = 255; }     // unused slots
+    cudaError_t e = cudaMemcpyToSymbol(c_pair_a, pa, sizeof pa);
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(c_pair_b, pb, sizeof pb);
+    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(select_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(Smem::total));
 }
@@ -405,6 +502,7 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     p.invn0 = a.invn0; p.invn1 = a.invn1; p.rows = a.rows; p.term_rows = a.term_rows; p.Q = a.Q;
     p.n0 = a.n0; p.n1 = a.n1; p.kp0 = a.kp0; p.kp1 = a.kp1; p.k = a.k; p.mult0 = a.mult0; p.mult1 = a.mult1;
     p.ids32 = a.ids32; p.weights = a.weights; p.ids64 = a.ids64; p.raw_scores = a.raw_scores; p.status = a.status;
+    p.overflow_rows = a.overflow_rows; p.overflow_count = a.overflow_count;
     const int64_t n_tiles = (a.rows + BM - 1) / BM;
     const unsigned grid = static_cast<unsigned>(n_tiles < a.sm_count ? n_tiles : a.sm_count);
     select_tc_kernel<<<grid, THREADS, Smem::total, s>>>(mq, mk0, mk1, p);
