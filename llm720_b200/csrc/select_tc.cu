@@ -226,7 +226,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // sorted lists of my 8 rows, per half: rows 0-3 in lanes 0-15, rows 4-7 in lanes 16-31
             float hv[2][4]; int hc[2][4];
             unsigned overflow = 0;                     // bit rr: row 8s+rr overflowed its candidate list
-#pragma unroll
+#pragma unroll 1
             for (int hf = 0; hf < 2; ++hf) {
                 const int n = hf ? p.n1 : p.n0;
                 const int nch = hf ? nch1 : nch0;
@@ -328,7 +328,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                 }
                 // the 16 best candidates of my 8 rows, in order (score descending, sub-key ascending)
-#pragma unroll
+#pragma unroll 1
                 for (int rb = 0; rb < 8; rb += 4) {          // four rows' networks side by side
                     float v[4]; int c[4];
                     unsigned pooled = 0;                     // bit q: the row's list continues in the pool
@@ -380,7 +380,9 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             v[q] = __shfl_sync(FULL_MASK, v[q], lane & 15);
                             c[q] = __shfl_sync(FULL_MASK, c[q], lane & 15);
                         }
-                        if ((rb != 0) == (half16 != 0)) { hv[hf][q] = v[q]; hc[hf][q] = c[q]; }
+                        if ((rb != 0) == (half16 != 0)) {
+                            if (hf == 0) { hv[0][q] = v[q]; hc[0][q] = c[q]; } else { hv[1][q] = v[q]; hc[1][q] = c[q]; }
+                        }
                     }
                 }
             }
@@ -390,7 +392,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             // only pairs with (a+1)(b+1) <= k can reach the top k: both lists are sorted
             const bool use0 = pa0 < p.kp0 && pb0 < p.kp1 && (pa0 + 1) * (pb0 + 1) <= p.k;
             const bool use1 = pa1 < p.kp0 && pb1 < p.kp1 && (pa1 + 1) * (pb1 + 1) <= p.k;
-#pragma unroll
+#pragma unroll 1
             for (int rb = 0; rb < 8; rb += 4) {              // four rows side by side
                 const int base = rb ? 16 : 0;                  // lane base + j: j-th best of each half
                 const int pos0 = pa0 * 16 + pb0, pos1 = pa1 * 16 + pb1;
