@@ -150,6 +150,20 @@ int peer_gather_eval_partial(peer_handle_t h, const void* x, const int32_t* ids,
                              const void* expert_up, const float* down_scale, const float* up_scale,
                              int64_t n_local_rows, float* out_f32, int64_t n_tokens, void* stream);
 
+/* Backward of peer_gather_eval: the gradients autograd derives for the expert evaluation of the
+ * reference (llm/models/experts.py:332-382; exercised by tests/test_peer_integration.py:181-192 and
+ * by the training step, llm/training/train.py:743-768).  Given grad_out = dL/dout [T, output_dim]
+ * (act_dtype) and the forward's x, ids and weights:
+ *   grad_x       [T, input_dim]      fp32, written:  sum_j dz_j * down[ids_j]
+ *   grad_weights [T, num_heads*top_k] fp32, written: act(down[ids_j] . x) * (up[ids_j] . grad_out)
+ *   grad_down    [num_experts, input_dim]  fp32, ACCUMULATED: += dz_j * x          (zero it first)
+ *   grad_up      [num_experts, output_dim] fp32, ACCUMULATED: += w_j * act(.) * grad_out
+ * with dz_j = w_j * (up[ids_j] . grad_out) * act'(down[ids_j] . x).  Tables must be in act_dtype. */
+int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
+                              const float* weights, const void* expert_down, const void* expert_up,
+                              float* grad_x, float* grad_weights, float* grad_down, float* grad_up,
+                              int64_t n_tokens, void* stream);
+
 /* Product-key retrieval (same result as peer_select) for callers that cannot allocate device
  * memory: no handle, no cudaMalloc anywhere on this path.  This entry point has no counterpart in
  * the reference; it exists for embedders that have given all GPU memory to their own pool, or that

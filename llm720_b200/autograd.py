@@ -1,0 +1,104 @@
+"""Differentiable PEER forward: the library's kernels for the values, and for
+the gradients of the expert stage; torch operations for the small rest.
+
+The reference trains through its PyTorch forward (llm/models/experts.py:
+288-384; llm/training/train.py:743-768), with autograd deriving every gradient.
+Here the stages are
+
+* query projection + LayerNorm: value from the library's query kernel (fp32);
+  gradient by re-running ``F.linear`` / ``F.layer_norm`` in backward
+  (``_ProjectQueries``);
+* product-key selection: the library's select kernel, no gradient (indices);
+  the reference reads the sub-keys through ``.data`` (experts.py:154), so they
+  receive no gradient there either;
+* the k selected scores per head are recomputed from the queries and the 2k
+  selected sub-key rows with torch operations (differentiable in the queries),
+  softmax, optional dropout of the expert activations (experts.py:366; a
+  per-slot factor, folded into the weights because each expert has one neuron);
+* expert evaluation: ``peer_gather_eval`` forward, ``peer_gather_eval_backward``
+  backward (``_ExpertEval``): dense fp32 table gradients accumulated with vector
+  reductions, cast to the parameters' dtype at the end.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+
+class _ProjectQueries(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, ln_w, ln_b, op, wdict, num_heads, query_dim):
+        ctx.save_for_backward(x, weight, bias, ln_w, ln_b)
+        ctx.shape = (num_heads, query_dim)
+        return op.project_queries(x, wdict)                    # [T, H, Q] fp32, after LayerNorm
+
+    @staticmethod
+    def backward(ctx, grad_q):
+        saved = ctx.saved_tensors
+        H, Q = ctx.shape
+        leaves = [None if t is None else t.detach().requires_grad_(need)
+                  for t, need in zip(saved, ctx.needs_input_grad[:5])]
+        x, weight, bias, ln_w, ln_b = leaves
+        with torch.enable_grad():
+            q = F.linear(x, weight, bias).float().view(x.shape[0], H, Q)
+            if ln_w is not None:
+                q = F.layer_norm(q, (Q,), ln_w.float(), None if ln_b is None else ln_b.float(), 1e-5)
+        wanted = [t for t in leaves if t is not None and t.requires_grad]
+        grads = iter(torch.autograd.grad(q, wanted, grad_q.contiguous())) if wanted else iter(())
+        out = [next(grads) if (t is not None and t.requires_grad) else None for t in leaves]
+        return (*out, None, None, None, None)
+
+
+class _ExpertEval(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weights, ids32, down, up, op):
+        ctx.save_for_backward(x, weights, ids32, down, up)
+        ctx.op = op
+        return op.gather_eval(x, ids32, weights.contiguous(), down, up)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weights, ids32, down, up = ctx.saved_tensors
+        gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up)
+        need = ctx.needs_input_grad
+        return (gx.to(x.dtype) if need[0] else None, gw if need[1] else None, None,
+                gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None)
+
+
+def peer_forward_autograd(module, hidden_states: torch.Tensor) -> torch.Tensor:
+    """Forward of ``module`` (a ``llm720_b200.PEER``) that records an autograd graph."""
+    w = module._weights()
+    if w["down_scale"] is not None:
+        raise RuntimeError("quantised (FP8) expert tables are inference-only: no backward pass")
+    dt = module.query_proj.weight.dtype
+    B, S, _ = hidden_states.shape
+    T = B * S
+    H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
+    n1 = module.product_key_dim[1]
+    x = hidden_states.contiguous().view(T, module.input_dim)
+    op = module._operator(x.device, dt, T)
+    ln = module.query_layer_norm
+    q = _ProjectQueries.apply(x, module.query_proj.weight, module.query_proj.bias,
+                              None if ln is None else ln.weight, None if ln is None else ln.bias, op, w, H, Q)
+    keys0, keys1 = module.sub_keys[0].detach(), module.sub_keys[1].detach()
+    with torch.no_grad():
+        pid, _ = module._product_operator(x.device, dt, T).select(q.detach(), keys0, keys1)   # i0 * n1 + i1
+        i0 = torch.div(pid, n1, rounding_mode="floor")
+        i1 = pid - i0 * n1
+        flat = (i0 + i1) if module.index_mode == "reference" else pid
+    hw = Q // 2
+    q0, q1 = q[..., :hw], q[..., hw:]
+    k0, k1 = keys0.float(), keys1.float()
+    if module.norm_keys:
+        k0, k1 = F.normalize(k0, dim=-1), F.normalize(k1, dim=-1)
+    if module.norm_query:
+        q0, q1 = F.normalize(q0, dim=-1), F.normalize(q1, dim=-1)
+    scores = (q0.unsqueeze(2) * k0[i0]).sum(-1) + (q1.unsqueeze(2) * k1[i1]).sum(-1)       # [T, H, k]
+    weights = torch.softmax(scores, dim=-1)
+    if module.training and module.dropout.p > 0:
+        weights = weights * F.dropout(torch.ones_like(weights), module.dropout.p, True)
+    out = _ExpertEval.apply(x, weights.view(T, H * k), flat.to(torch.int32).view(T, H * k),
+                            module.expert_down.weight, module.expert_up.weight, op)
+    if module.track_indices:
+        module._stash(flat, scores.detach(), B, S)
+    return out.view(B, S, module.output_dim)

@@ -108,6 +108,28 @@ struct GatherArgs {
     float* out_f32;           // optional fp32 output [T, Dout] (partial sums of a row-sharded table)
 };
 cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s);
+
+// Backward of the expert evaluation (gather_grad.cu): fp32 or bf16 layers with tables of the same dtype.
+struct GatherGradArgs {
+    const void* x;            // [T, D] act dtype
+    const void* dy;           // [T, Dout] act dtype
+    const int32_t* ids;       // [T, HK]
+    const float* weights;     // [T, HK]
+    const void* down;         // [N, D]
+    const void* up;           // [N, Dout]
+    float* d_down;            // [N, D] fp32, accumulated into
+    float* d_up;              // [N, Dout] fp32, accumulated into
+    float* dx;                // [T, D] fp32, written
+    float* dweights;          // [T, HK] fp32, written
+    int64_t T;
+    int HK;
+    int64_t N;
+    int D, Dout;
+    int act_dtype, table_dtype, activation;
+    int* status;
+    int sm_count;
+};
+cudaError_t launch_gather_grad(const GatherGradArgs& a, cudaStream_t s);
 // one-time per-process attribute set-up (dynamic shared memory opt-in)
 cudaError_t gather_eval_setup();
 cudaError_t select_simt_setup();

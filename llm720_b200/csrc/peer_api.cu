@@ -580,6 +580,35 @@ extern "C" int peer_gather_eval_partial(peer_handle_t h, const void* x, const in
     return PEER_OK;
 }
 
+extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
+                                         const float* weights, const void* expert_down, const void* expert_up,
+                                         float* grad_x, float* grad_weights, float* grad_down, float* grad_up,
+                                         int64_t n_tokens, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    const peer_config_t& c = h->cfg;
+    if (!x || !grad_out || !ids || !weights || !expert_down || !expert_up || !grad_x || !grad_weights || !grad_down || !grad_up)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_backward: null pointer");
+    if (c.table_dtype != c.act_dtype)
+        return fail(h, PEER_ERR_UNSUPPORTED, "backward needs tables in the layer's dtype (fp32 or bf16); quantised tables are inference-only");
+    if (!aligned16(x) || !aligned16(grad_out) || !aligned16(expert_down) || !aligned16(expert_up) || !aligned16(grad_x) ||
+        !aligned16(grad_down) || !aligned16(grad_up))
+        return fail(h, PEER_ERR_INVALID_ARG, "x, grad_out, tables and gradient buffers must be 16-byte aligned");
+    GatherGradArgs g{};
+    g.x = x; g.dy = grad_out; g.ids = ids; g.weights = weights; g.down = expert_down; g.up = expert_up;
+    g.d_down = grad_down; g.d_up = grad_up; g.dx = grad_x; g.dweights = grad_weights;
+    g.T = n_tokens; g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
+    g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
+    g.status = h->status; g.sm_count = h->sm_count;
+    cudaError_t e = launch_gather_grad(g, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue)
+        return fail(h, PEER_ERR_UNSUPPORTED, "expert backward: row width %d/%d is not implemented for this dtype (bf16 up to 2048, fp32 up to 1024)",
+                    c.input_dim, c.output_dim);
+    CU_TRY(h, e);
+    h->launches += 1;
+    return PEER_OK;
+}
+
 extern "C" int peer_query_status(peer_handle_t h, void* stream) {
     if (!h) return PEER_ERR_INVALID_ARG;
     cudaStream_t s = static_cast<cudaStream_t>(stream);

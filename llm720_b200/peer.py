@@ -200,6 +200,31 @@ class PeerOp:
                 _ptr(down_scale), _ptr(up_scale), down.shape[0], _ptr(out), T, _stream(self.device)))
         return out
 
+    def gather_eval_backward(self, x, grad_out, ids32, weights, down, up, grad_down=None, grad_up=None):
+        """Gradients of ``gather_eval``.  Returns (grad_x [T,D] fp32, grad_weights [T,H*k] fp32, grad_down
+        [N,D] fp32, grad_up [N,D_out] fp32); the two table gradients are accumulated into the buffers
+        passed in (zero-initialised ones are made when none are given)."""
+        self._dev(x, "x", self.act_dtype)
+        self._dev(grad_out, "grad_out", self.act_dtype)
+        self._dev(ids32, "ids", torch.int32)
+        self._dev(weights, "weights", torch.float32)
+        self._dev(down, "expert_down", self.table_dtype)
+        self._dev(up, "expert_up", self.table_dtype)
+        T = x.shape[0]
+        if grad_down is None:
+            grad_down = torch.zeros(down.shape, dtype=torch.float32, device=self.device)
+        if grad_up is None:
+            grad_up = torch.zeros(up.shape, dtype=torch.float32, device=self.device)
+        self._dev(grad_down, "grad_down", torch.float32)
+        self._dev(grad_up, "grad_up", torch.float32)
+        gx = torch.empty(T, self.cfg.input_dim, dtype=torch.float32, device=self.device)
+        gw = torch.empty(T, self.cfg.num_heads * self.cfg.top_k, dtype=torch.float32, device=self.device)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_gather_eval_backward(
+                self.handle, _ptr(x), _ptr(grad_out), _ptr(ids32), _ptr(weights), _ptr(down), _ptr(up),
+                _ptr(gx), _ptr(gw), _ptr(grad_down), _ptr(grad_up), T, _stream(self.device)))
+        return gx, gw, grad_down, grad_up
+
     def query_status(self):
         """Synchronise and raise if a kernel recorded a timeout or an out-of-range id."""
         with torch.cuda.device(self.device):
@@ -289,6 +314,8 @@ class PEER(nn.Module):
         self._last_expert_scores: Optional[torch.Tensor] = None
         self._op: Optional[PeerOp] = None
         self._op_key = None
+        self._sel_op: Optional[PeerOp] = None
+        self._sel_op_key = None
 
     # -- FP8 tables ---------------------------------------------------------
     @torch.no_grad()
@@ -320,7 +347,8 @@ class PEER(nn.Module):
         if self._op is None or self._op_key != key or self._op.cfg.max_tokens < cap:
             if self._op is not None:
                 cap = max(cap, self._op.cfg.max_tokens) if self._op_key == key else cap
-                self._op.close()
+                # not closed here: an autograd graph may still hold the old handle; it is released with
+                # its last reference
             self._op = PeerOp(input_dim=self.input_dim, output_dim=self.output_dim, num_heads=self.num_heads,
                               query_dim=self.query_dim, product_key_dim=self.product_key_dim,
                               top_k=self.num_experts_per_tok, act_dtype=act_dtype, table_dtype=table_dtype,
@@ -330,14 +358,30 @@ class PEER(nn.Module):
             self._op_key = key
         return self._op
 
+    def _product_operator(self, device, act_dtype, n_tokens: int) -> PeerOp:
+        """A second handle whose selection returns i0 * n1 + i1 whatever ``index_mode`` is: the
+        differentiable forward needs both sub-key indices of every selected expert."""
+        if self.index_mode == "product":
+            return self._operator(device, act_dtype, n_tokens)
+        cap = min(max(n_tokens, 1), self.max_slice_tokens)
+        key = (str(device), act_dtype, self.norm_keys, self.norm_query)
+        if self._sel_op is None or self._sel_op_key != key or self._sel_op.cfg.max_tokens < cap:
+            self._sel_op = PeerOp(input_dim=self.input_dim, output_dim=self.output_dim, num_heads=self.num_heads,
+                                  query_dim=self.query_dim, product_key_dim=self.product_key_dim,
+                                  top_k=self.num_experts_per_tok, act_dtype=act_dtype, table_dtype=act_dtype,
+                                  activation=self.activation_name, norm_keys=self.norm_keys,
+                                  norm_query=self.norm_query, layer_norm=self.batch_norm_query,
+                                  index_mode="product", max_tokens=cap, device=device)
+            self._sel_op_key = key
+        return self._sel_op
+
+    def _needs_grad(self, hidden_states: torch.Tensor) -> bool:
+        return torch.is_grad_enabled() and (hidden_states.requires_grad or
+                                            any(p.requires_grad for p in self.parameters()))
+
     def _prepare(self, hidden_states: torch.Tensor):
         if hidden_states.dim() != 3 or hidden_states.shape[-1] != self.input_dim:
             raise ValueError(f"hidden_states must be [batch, seq, {self.input_dim}], got {tuple(hidden_states.shape)}")
-        if self.training and self.dropout.p > 0:
-            raise RuntimeError("peer_b200 is a forward (inference) path: dropout in training mode is not implemented")
-        if torch.is_grad_enabled() and (hidden_states.requires_grad or any(p.requires_grad for p in self.parameters())):
-            raise RuntimeError("peer_b200 implements the forward pass only; call it under torch.no_grad() "
-                               "(or freeze the parameters)")
         w = self._weights()
         dt = self.query_proj.weight.dtype
         if hidden_states.dtype != dt:
@@ -346,11 +390,20 @@ class PEER(nn.Module):
 
     # -- forward --------------------------------------------------------------
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
-        """[batch, seq, input_dim] -> [batch, seq, output_dim], same dtype (experts.py:422-440)."""
+        """[batch, seq, input_dim] -> [batch, seq, output_dim], same dtype (experts.py:422-440).
+        When gradients are being recorded the call goes through ``autograd.peer_forward_autograd``;
+        dropout (training mode, experts.py:366) exists on that path only."""
         w, dt = self._prepare(hidden_states)
+        grad = self._needs_grad(hidden_states)
+        if not grad and self.training and self.dropout.p > 0:
+            raise RuntimeError("dropout in training mode needs the differentiable path: enable gradients, "
+                               "or call eval()")
         if hidden_states.device.type != "cuda":
             raise RuntimeError("peer_b200 runs on CUDA devices only (sm_100a); there is no CPU path. "
                                "Use forward_host() to feed pinned host buffers.")
+        if grad:
+            from .autograd import peer_forward_autograd
+            return peer_forward_autograd(self, hidden_states)
         B, S, _ = hidden_states.shape
         T = B * S
         x = hidden_states.contiguous().view(T, self.input_dim)
@@ -366,7 +419,11 @@ class PEER(nn.Module):
 
     def forward_host(self, hidden_states: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Same layer for a HOST tensor (pinned for full speed): slices are copied to the device,
-        processed and copied back on overlapping streams.  Returns a host tensor."""
+        processed and copied back on overlapping streams.  Returns a host tensor.  Inference only."""
+        if self._needs_grad(hidden_states):
+            raise RuntimeError("forward_host is an inference path; call it under torch.no_grad()")
+        if self.training and self.dropout.p > 0:
+            raise RuntimeError("forward_host is an inference path: call eval() first (dropout is set)")
         w, dt = self._prepare(hidden_states)
         if hidden_states.device.type != "cpu":
             raise RuntimeError("forward_host takes a host tensor")

@@ -74,3 +74,33 @@ def make_op(cfg: syn.PeerConfig, device, index_mode="reference", max_tokens=None
                   query_dim=cfg.query_dim, product_key_dim=cfg.product_key_dim, top_k=cfg.top_k,
                   act_dtype=cfg.dtype, table_dtype=table_dtype or cfg.table_dtype, index_mode=index_mode,
                   max_tokens=max_tokens or max(cfg.tokens, 1), device=device, **kw)
+
+
+GRAD_DENSE = ("x", "query_proj.weight", "query_proj.bias", "query_layer_norm.weight", "query_layer_norm.bias")
+GRAD_TABLES = ("expert_down.weight", "expert_up.weight")
+
+
+def load_golden_grads(name: str):
+    """Golden gradients written by tests/golden/make_golden_grads.py: (grad_out, {name: dense gradient},
+    {table name: (row ids, rows)})."""
+    rec = np.load(os.path.join(GOLDEN, name + "_grads.npz"))
+    dense = {k: torch.from_numpy(rec["g:" + k]) for k in GRAD_DENSE}
+    tables = {k: (torch.from_numpy(rec["rows:" + k].astype(np.int64)), torch.from_numpy(rec["g:" + k]))
+              for k in GRAD_TABLES}
+    return torch.from_numpy(rec["grad_out"]), dense, tables
+
+
+def oracle_gradients(cfg, sd, x, grad_out, index_mode="reference", dtype=torch.float32):
+    """Autograd through the oracle forward: {name: gradient} for x, the dense weights and both tables."""
+    leaf = {k: v.to(dtype).clone().requires_grad_(True) for k, v in sd.items()}
+    xl = x.to(dtype).clone().requires_grad_(True)
+    out, _, _ = orc.forward(xl, oracle_weights(leaf, dtype), oracle_shape(cfg), index_mode)
+    out.backward(grad_out.to(dtype))
+    g = {k: v.grad for k, v in leaf.items()}
+    g["x"] = xl.grad
+    return g
+
+
+def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
+    """Largest absolute difference relative to the largest reference entry."""
+    return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))

@@ -73,11 +73,13 @@ def test_rejects_what_the_kernels_do_not_implement():
         PEER(32, 32, 64, expert_hidden_size=2, product_key_dim=[8, 8])
 
 
-def test_no_cpu_path_and_no_silent_autograd():
+def test_no_cpu_path():
     m = small().eval()
     x = torch.randn(2, 3, 32)
-    with pytest.raises(RuntimeError, match="forward pass only"):
-        m(x)                                   # parameters require grad, grad mode on
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        m(x)                                   # parameters require grad, grad mode on: still no CPU path
+    with pytest.raises(RuntimeError, match="inference path"):
+        m.forward_host(x)
     with torch.no_grad():
         with pytest.raises(RuntimeError, match="no CPU path"):
             m(x)
