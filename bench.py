@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--backward", action="store_true",
+                    help="also time forward+backward (training step of the layer) and add a 'backward' object")
     return ap.parse_args()
 
 
@@ -160,6 +162,52 @@ def make_layer(cfg, args, device):
     m.eval().requires_grad_(False)
     m.index_mode = args.index_mode
     return m, sd
+
+
+def time_backward(layer, cfg, x, steps):
+    """Forward+backward of the layer (all parameters and x require gradients), and the expert-stage
+    gradient kernel on its own.  Algorithmic bytes of that kernel per (token, slot): the two table rows
+    read, and the two fp32 gradient rows read and written."""
+    T, HK = cfg.tokens, cfg.num_heads * cfg.top_k
+    layer.requires_grad_(True)
+    xg = x.clone().requires_grad_(True)
+    gen = torch.Generator(device=x.device).manual_seed(1)
+    grad_out = torch.randn(x.shape[0], x.shape[1], cfg.output_dim, generator=gen, device=x.device).to(cfg.dtype)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    for i in range(2 + steps):
+        if i == 2:
+            torch.cuda.synchronize()
+            ev[0].record()
+        layer.zero_grad(set_to_none=True)
+        xg.grad = None
+        layer(xg).backward(grad_out)
+    ev[1].record()
+    torch.cuda.synchronize()
+    step_ms = ev[0].elapsed_time(ev[1]) / steps
+    layer.zero_grad(set_to_none=True)
+    layer.requires_grad_(False)
+    # the kernel alone, on the selections of the last forward
+    op = layer._op
+    ids = layer._last_expert_indices.view(T, HK).to(torch.int32)
+    w = torch.softmax(layer._last_expert_scores.view(T, cfg.num_heads, cfg.top_k), -1).view(T, HK).contiguous()
+    gd = torch.zeros(layer.expert_down.weight.shape, dtype=torch.float32, device=x.device)
+    gu = torch.zeros(layer.expert_up.weight.shape, dtype=torch.float32, device=x.device)
+    x2, g2 = x.view(T, -1), grad_out.view(T, -1)
+    for i in range(1 + 3):
+        if i == 1:
+            ev[2].record()
+        op.gather_eval_backward(x2, g2, ids, w, layer.expert_down.weight, layer.expert_up.weight, gd, gu)
+    ev[3].record()
+    torch.cuda.synchronize()
+    op.query_status()
+    k_ms = ev[2].elapsed_time(ev[3]) / 3
+    eb = torch.empty(0, dtype=cfg.table_dtype).element_size()
+    bytes_alg = T * HK * (cfg.input_dim + cfg.output_dim) * (eb + 8)
+    peak, kind = hbm_peak()
+    return {"fwd_bwd_ms_per_step": step_ms, "fwd_bwd_tokens_per_s": T / (step_ms / 1e3), "steps": steps,
+            "gather_grad_kernel_ms": k_ms, "algorithmic_bytes_per_launch": bytes_alg,
+            "achieved_GBps": bytes_alg / (k_ms / 1e3) / 1e9, "frac_of_hbm_peak": bytes_alg / (k_ms / 1e3) / 1e9 / peak,
+            "peak_kind": kind}
 
 
 def main():
@@ -268,6 +316,9 @@ def main():
                "h2d_bytes_per_step": xh.numel() * xh.element_size() * world,
                "d2h_bytes_per_step": outh.numel() * outh.element_size() * world,
                "api": "PEER.forward_host -> peer_forward_host (C ABI), pinned host buffers"}
+    backward = None
+    if args.backward and cfg.table_dtype != torch.float8_e4m3fn:
+        backward = time_backward(layer, cfg, x, min(args.steps, 5))
     clocks = sampler.stop() if sampler is not None else None
 
     if rank != 0:
@@ -300,7 +351,8 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload,
-        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks}))
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches, "clocks": clocks,
+        **({"backward": backward} if backward else {})}))
     if dist is not None:
         dist.destroy_process_group()
 
