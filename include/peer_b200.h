@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define PEER_B200_ABI_VERSION 1
+#define PEER_B200_ABI_VERSION 2
 
 /* Return codes.  Nothing in this library falls back to another code path:
  * an unsupported configuration is an error. */
@@ -53,14 +53,17 @@ typedef struct peer_config {
     int32_t top_k;              /* num_experts_per_tok, <= 32                         */
     int32_t num_heads;
     int32_t query_dim;          /* per head, even, <= 256                             */
-    int32_t n_keys0, n_keys1;   /* product_key_dim (two dimensions only)              */
-    int32_t expert_hidden_size; /* must be 1                                          */
+    int32_t n_keys0, n_keys1;   /* product_key_dim[0], [1]                            */
+    int32_t expert_hidden_size; /* neurons per expert, 1..16 (experts.py:337-352: down rows are
+                                   [h, input_dim] blocks, up rows [output_dim, h] blocks)           */
     int32_t activation;         /* PEER_ACT_*                                         */
     int32_t norm_keys, norm_query, layer_norm; /* booleans (batch_norm_query = layer_norm) */
     int32_t act_dtype;          /* dtype of x, out, query weights, LN affine, sub-keys: F32 or BF16 */
     int32_t table_dtype;        /* dtype of expert_down / expert_up: F32, BF16 or E4M3 */
     int32_t index_mode;         /* PEER_INDEX_*                                       */
     int64_t max_tokens;         /* scratch capacity; longer inputs are processed in slices */
+    int32_t num_key_dims;       /* len(product_key_dim): 1..4; 0 is read as 2         */
+    int32_t n_keys2, n_keys3;   /* product_key_dim[2], [3] (read when num_key_dims says so) */
 } peer_config_t;
 
 /* Tensors of one forward call; all row-major and contiguous.
@@ -81,6 +84,8 @@ typedef struct peer_tensors {
     void*        out;          /* [T, output_dim]                act_dtype            */
     int64_t*     ids_out;      /* optional [T, num_heads, top_k]: selected expert ids */
     float*       scores_out;   /* optional [T, num_heads, top_k]: raw (pre-softmax) scores */
+    const void*  keys2;        /* [n_keys2, query_dim/num_key_dims] (3-D, 4-D key grids) */
+    const void*  keys3;        /* [n_keys3, query_dim/num_key_dims] (4-D key grids)      */
 } peer_tensors_t;
 
 typedef struct peer_op* peer_handle_t;
@@ -130,6 +135,12 @@ int peer_project_queries(peer_handle_t h, const peer_tensors_t* t, int64_t n_tok
  * both [T, num_heads, top_k], sorted by descending score. */
 int peer_select(peer_handle_t h, const float* queries, const void* keys0, const void* keys1,
                 int64_t n_tokens, int64_t* ids_out, float* scores_out, void* stream);
+
+/* Same retrieval for a key grid of any dimensionality (1 to 4; experts.py:195-270: the dimensions
+ * are folded in one at a time and all but the last fold keep the best 4*top_k sums).  `keys` is an
+ * array of num_key_dims device pointers, table d being [n_keys_d, query_dim/num_key_dims]. */
+int peer_select_nd(peer_handle_t h, const float* queries, const void* const* keys, int64_t n_tokens,
+                   int64_t* ids_out, float* scores_out, void* stream);
 
 /* Expert evaluation from given selections: experts.py:327-382 with the
  * softmax already applied.  ids int32 and weights fp32, both

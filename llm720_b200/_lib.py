@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libpeer_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_BOUNDS = range(6)
 DTYPE_F32, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2
 ACT_GELU, ACT_RELU = 0, 1
@@ -24,13 +24,14 @@ class PeerConfig(C.Structure):
         ("expert_hidden_size", C.c_int32), ("activation", C.c_int32), ("norm_keys", C.c_int32),
         ("norm_query", C.c_int32), ("layer_norm", C.c_int32), ("act_dtype", C.c_int32),
         ("table_dtype", C.c_int32), ("index_mode", C.c_int32), ("max_tokens", C.c_int64),
+        ("num_key_dims", C.c_int32), ("n_keys2", C.c_int32), ("n_keys3", C.c_int32),
     ]
 
 
 class PeerTensors(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "x", "query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1", "expert_down", "expert_up",
-        "down_scale", "up_scale", "out", "ids_out", "scores_out")]
+        "down_scale", "up_scale", "out", "ids_out", "scores_out", "keys2", "keys3")]
 
 
 EXPORTS = {
@@ -43,6 +44,8 @@ EXPORTS = {
     "peer_project_queries": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                               C.c_void_p, C.c_void_p]),
+    "peer_select_nd": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int64, C.c_void_p, C.c_void_p,
+                                 C.c_void_p]),
     "peer_select_noalloc": (C.c_int, [C.POINTER(PeerConfig), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
     "peer_gather_eval": (C.c_int, [C.c_void_p] * 9 + [C.c_int64, C.c_void_p]),

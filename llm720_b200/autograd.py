@@ -74,28 +74,44 @@ def peer_forward_autograd(module, hidden_states: torch.Tensor) -> torch.Tensor:
     B, S, _ = hidden_states.shape
     T = B * S
     H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
-    n1 = module.product_key_dim[1]
+    dims = list(module.product_key_dim)
+    nd = len(dims)
+    strides = [1] * nd                                      # true row-major strides of the key grid
+    for d in range(nd - 2, -1, -1):
+        strides[d] = strides[d + 1] * dims[d + 1]
     x = hidden_states.contiguous().view(T, module.input_dim)
     op = module._operator(x.device, dt, T)
     ln = module.query_layer_norm
     q = _ProjectQueries.apply(x, module.query_proj.weight, module.query_proj.bias,
                               None if ln is None else ln.weight, None if ln is None else ln.bias, op, w, H, Q)
-    keys0, keys1 = module.sub_keys[0].detach(), module.sub_keys[1].detach()
+    keys = [p.detach() for p in module.sub_keys]
     with torch.no_grad():
-        pid, _ = module._product_operator(x.device, dt, T).select(q.detach(), keys0, keys1)   # i0 * n1 + i1
-        i0 = torch.div(pid, n1, rounding_mode="floor")
-        i1 = pid - i0 * n1
-        flat = (i0 + i1) if module.index_mode == "reference" else pid
-    hw = Q // 2
-    q0, q1 = q[..., :hw], q[..., hw:]
-    k0, k1 = keys0.float(), keys1.float()
-    if module.norm_keys:
-        k0, k1 = F.normalize(k0, dim=-1), F.normalize(k1, dim=-1)
-    if module.norm_query:
-        q0, q1 = F.normalize(q0, dim=-1), F.normalize(q1, dim=-1)
-    scores = (q0.unsqueeze(2) * k0[i0]).sum(-1) + (q1.unsqueeze(2) * k1[i1]).sum(-1)       # [T, H, k]
+        sel = module._product_operator(x.device, dt, T)
+        if nd == 2:
+            pid, _ = sel.select(q.detach(), keys[0], keys[1])                  # sum_d i_d * stride_d
+        else:
+            pid, _ = sel.select_nd(q.detach(), keys)
+        idx = [torch.div(pid, strides[d], rounding_mode="floor") % dims[d] for d in range(nd)]
+        if module.index_mode == "reference" and nd > 1:      # the first dimension loses its multiplier
+            flat = idx[0] + sum(idx[d] * strides[d] for d in range(1, nd))
+        elif module.index_mode == "reference":               # 1-D: positions in the candidate list (experts.py:197-200)
+            flat = torch.arange(k, device=pid.device).expand_as(pid).contiguous()
+        else:
+            flat = pid
+    width = Q // nd
+    scores = 0
+    for d in range(nd):
+        qd = q[..., d * width:(d + 1) * width]
+        kd = keys[d].float()
+        if module.norm_keys:
+            kd = F.normalize(kd, dim=-1)
+        if module.norm_query:
+            qd = F.normalize(qd, dim=-1)
+        scores = scores + (qd.unsqueeze(2) * kd[idx[d]]).sum(-1)                # [T, H, k]
     weights = torch.softmax(scores, dim=-1)
     if module.training and module.dropout.p > 0:
+        if module.expert_hidden_size != 1:
+            raise RuntimeError("dropout with expert_hidden_size > 1 is not implemented (it acts on every neuron)")
         weights = weights * F.dropout(torch.ones_like(weights), module.dropout.p, True)
     out = _ExpertEval.apply(x, weights.view(T, H * k), flat.to(torch.int32).view(T, H * k),
                             module.expert_down.weight, module.expert_up.weight, op)

@@ -104,6 +104,7 @@ struct GatherArgs {
     int act_dtype, table_dtype, activation;
     int* status;              // device status word
     int sm_count;
+    int hidden;               // neurons per expert (rows are [hidden, D] / [Dout, hidden] blocks); 0 or 1 = single
     const int32_t* counts;    // optional [T]: how many of token t's HK entries are in use
     float* out_f32;           // optional fp32 output [T, Dout] (partial sums of a row-sharded table)
 };
@@ -128,8 +129,31 @@ struct GatherGradArgs {
     int act_dtype, table_dtype, activation;
     int* status;
     int sm_count;
+    int hidden;               // neurons per expert; 0 or 1 = single
 };
 cudaError_t launch_gather_grad(const GatherGradArgs& a, cudaStream_t s);
+
+// Experts with several hidden neurons (gather_hidden.cu): forward and backward, fp32 or bf16 layers
+// with tables of the same dtype.
+cudaError_t launch_gather_hidden(const GatherArgs& a, cudaStream_t s);
+cudaError_t launch_gather_hidden_grad(const GatherGradArgs& a, cudaStream_t s);
+
+// Product-key selection over 1 to 4 key dimensions (select_nd.cu).
+struct SelectNdArgs {
+    const float* q_ln;        // [rows, Q] fp32 queries after LayerNorm
+    const void* keys[4];      // [n[d], Q/nd] act dtype, as stored
+    int n[4];
+    int kp[4];                // candidates kept per dimension (<= 32)
+    long long mult[4];        // flat id = sum_d index_d * mult[d]
+    int nd, Q, k;
+    int norm_keys, norm_query, act_dtype;
+    int64_t rows;
+    int32_t* ids32;           // optional [rows, k]
+    float* weights;           // optional [rows, k] softmax
+    int64_t* ids64;           // optional [rows, k]
+    float* raw_scores;        // optional [rows, k]
+};
+cudaError_t launch_select_nd(const SelectNdArgs& a, cudaStream_t s);
 // one-time per-process attribute set-up (dynamic shared memory opt-in)
 cudaError_t gather_eval_setup();
 cudaError_t select_simt_setup();

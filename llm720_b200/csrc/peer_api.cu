@@ -20,6 +20,13 @@ struct peer_op {
     int kp0 = 0, kp1 = 0, k_final = 0;
     int mult0 = 1, mult1 = 1;
     int n_pairs = 0;
+    // general form: any number of key dimensions, any number of neurons per expert
+    int nd = 2;
+    int n[4] = {0, 0, 0, 0};
+    int kp[4] = {0, 0, 0, 0};
+    long long mult[4] = {1, 1, 1, 1};
+    bool general_select = false;  // key grid that is not two-dimensional: select_nd.cu
+    int hidden = 1;
     // device scratch
     float* khat0 = nullptr;       // [Q/2, n0] normalised sub-keys, transposed
     float* khat1 = nullptr;       // [Q/2, n1]
@@ -78,9 +85,9 @@ void set_global_error(const char* msg) { g_create_error = msg ? msg : ""; }
 static int act_bytes(int dt) { return dt == PEER_DTYPE_F32 ? 4 : (dt == PEER_DTYPE_BF16 ? 2 : 1); }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// k' of the reference (llm/models/experts.py:168-187), two key dimensions.
-static int candidates_per_dim(int top_k, int dim_size) {
-    const int base = static_cast<int>(std::ceil(std::pow(static_cast<double>(top_k), 0.5))) + 2;
+// k' of the reference (llm/models/experts.py:168-187).
+static int candidates_per_dim(int top_k, int dim_size, int num_dims = 2) {
+    const int base = static_cast<int>(std::ceil(std::pow(static_cast<double>(top_k), 1.0 / num_dims))) + 2;
     int kp = base < dim_size ? base : dim_size;
     const int want = dim_size >= top_k ? top_k : dim_size;
     if (kp < want) kp = want;
@@ -120,9 +127,15 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     if (c->abi_version != PEER_B200_ABI_VERSION)
         return fail(nullptr, PEER_ERR_INVALID_ARG, "peer_create: abi_version %d, library has %d",
                     c->abi_version, PEER_B200_ABI_VERSION);
-    if (c->expert_hidden_size != 1)
-        return fail(nullptr, PEER_ERR_UNSUPPORTED, "expert_hidden_size=%d: only single-neuron experts (1) are implemented",
+    if (c->expert_hidden_size < 1 || c->expert_hidden_size > 16)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "expert_hidden_size=%d: 1 to 16 neurons per expert are implemented",
                     c->expert_hidden_size);
+    if (c->expert_hidden_size > 1 && c->table_dtype != c->act_dtype)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "experts with several neurons need tables in the layer's dtype");
+    const int nd = c->num_key_dims == 0 ? 2 : c->num_key_dims;
+    if (nd < 1 || nd > 4)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "num_key_dims=%d: 1 to 4 key dimensions are implemented", nd);
+    const int nkeys[4] = {c->n_keys0, nd > 1 ? c->n_keys1 : 1, nd > 2 ? c->n_keys2 : 1, nd > 3 ? c->n_keys3 : 1};
     if (c->activation != PEER_ACT_GELU && c->activation != PEER_ACT_RELU)
         return fail(nullptr, PEER_ERR_UNSUPPORTED, "activation %d is not implemented", c->activation);
     if (c->act_dtype != PEER_DTYPE_F32 && c->act_dtype != PEER_DTYPE_BF16)
@@ -132,16 +145,17 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     if (!combo)
         return fail(nullptr, PEER_ERR_UNSUPPORTED, "unsupported dtype pair: act %d, table %d (fp32/fp32, bf16/bf16, bf16/e4m3)",
                     c->act_dtype, c->table_dtype);
-    if (c->input_dim <= 0 || c->output_dim <= 0 || c->num_heads <= 0 || c->top_k <= 0 || c->n_keys0 <= 0 ||
-        c->n_keys1 <= 0 || c->query_dim <= 0 || c->max_tokens <= 0)
+    if (c->input_dim <= 0 || c->output_dim <= 0 || c->num_heads <= 0 || c->top_k <= 0 || nkeys[0] <= 0 ||
+        nkeys[1] <= 0 || nkeys[2] <= 0 || nkeys[3] <= 0 || c->query_dim <= 0 || c->max_tokens <= 0)
         return fail(nullptr, PEER_ERR_INVALID_ARG, "peer_create: non-positive dimension");
-    if (static_cast<int64_t>(c->n_keys0) * c->n_keys1 != c->num_experts)
-        return fail(nullptr, PEER_ERR_INVALID_ARG, "product of key dimensions %d x %d must equal num_experts %lld",
-                    c->n_keys0, c->n_keys1, static_cast<long long>(c->num_experts));
+    if (static_cast<int64_t>(nkeys[0]) * nkeys[1] * nkeys[2] * nkeys[3] != c->num_experts)
+        return fail(nullptr, PEER_ERR_INVALID_ARG, "product of key dimensions %d x %d x %d x %d must equal num_experts %lld",
+                    nkeys[0], nkeys[1], nkeys[2], nkeys[3], static_cast<long long>(c->num_experts));
     if (c->num_experts > 0x7fffffffLL)
         return fail(nullptr, PEER_ERR_UNSUPPORTED, "num_experts above 2^31-1");
-    if (c->query_dim % 2 || c->query_dim > 256)
-        return fail(nullptr, PEER_ERR_UNSUPPORTED, "query_dim=%d: must be even and <= 256", c->query_dim);
+    if (c->query_dim % nd || c->query_dim > 256)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "query_dim=%d: must be a multiple of the %d key dimensions and <= 256",
+                    c->query_dim, nd);
     if (c->input_dim % 8)
         return fail(nullptr, PEER_ERR_UNSUPPORTED, "input_dim=%d: must be a multiple of 8", c->input_dim);
     const int tb = act_bytes(c->table_dtype);
@@ -165,6 +179,49 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     h->cfg = *c;
     h->device = dev;
     h->sm_count = prop.multiProcessorCount;
+    h->nd = nd;
+    h->hidden = c->expert_hidden_size;
+    h->general_select = nd != 2;
+    {   // per-dimension candidate counts, id strides, and how many entries the folds leave
+        long long len = 0;
+        for (int d = 0; d < nd; ++d) {
+            h->n[d] = nkeys[d];
+            h->kp[d] = candidates_per_dim(c->top_k, nkeys[d], nd);
+            if (h->kp[d] > 32) { delete h; return fail(nullptr, PEER_ERR_UNSUPPORTED, "more than 32 candidates per key dimension"); }
+            if (d == 0) len = nd == 1 ? (c->top_k < h->kp[0] ? c->top_k : h->kp[0]) : h->kp[0];
+            else {
+                const long long count = len * h->kp[d];
+                const long long keep = d < nd - 1 ? 4LL * c->top_k : c->top_k;
+                len = keep < count ? keep : count;
+            }
+        }
+        h->mult[nd - 1] = 1;
+        for (int d = nd - 2; d >= 0; --d) h->mult[d] = h->mult[d + 1] * nkeys[d + 1];
+        if (c->index_mode == PEER_INDEX_REFERENCE) h->mult[0] = nd == 1 ? 0 : 1;   // llm/models/experts.py:203-204; 1-D: :197-200
+        if (len < c->top_k) {
+            delete h;
+            return fail(nullptr, PEER_ERR_UNSUPPORTED, "top_k=%d exceeds the %lld candidates this key grid yields",
+                        c->top_k, len);
+        }
+    }
+    if (h->general_select) {
+        h->k_final = c->top_k;
+        const int64_t HKg = static_cast<int64_t>(c->num_heads) * c->top_k;
+        cudaError_t eg = cudaMalloc(reinterpret_cast<void**>(&h->q_hat), sizeof(float) * c->max_tokens * c->num_heads * c->query_dim);
+        if (eg == cudaSuccess) eg = cudaMalloc(reinterpret_cast<void**>(&h->sel_ids), sizeof(int32_t) * c->max_tokens * HKg);
+        if (eg == cudaSuccess) eg = cudaMalloc(reinterpret_cast<void**>(&h->sel_w), sizeof(float) * c->max_tokens * HKg);
+        if (eg == cudaSuccess) eg = cudaMalloc(reinterpret_cast<void**>(&h->status), sizeof(int));
+        if (eg == cudaSuccess) eg = cudaMemset(h->status, 0, sizeof(int));
+        if (eg == cudaSuccess) eg = gather_eval_setup();
+        if (eg != cudaSuccess) {
+            fail(nullptr, PEER_ERR_CUDA, "peer_create: %s", cudaGetErrorString(eg));
+            free_all(h);
+            delete h;
+            return PEER_ERR_CUDA;
+        }
+        *out = h;
+        return PEER_OK;
+    }
     h->kp0 = candidates_per_dim(c->top_k, c->n_keys0);
     h->kp1 = candidates_per_dim(c->top_k, c->n_keys1);
     if (h->kp0 > 32 || h->kp1 > 32) { delete h; return fail(nullptr, PEER_ERR_UNSUPPORTED, "more than 32 candidates per half"); }
@@ -238,8 +295,8 @@ extern "C" int peer_destroy(peer_handle_t h) {
 static int check_tensors(peer_op* h, const peer_tensors_t* t, bool need_tables) {
     const peer_config_t& c = h->cfg;
     if (!t) return fail(h, PEER_ERR_INVALID_ARG, "null tensor struct");
-    if (!t->x || !t->query_w || !t->keys0 || !t->keys1)
-        return fail(h, PEER_ERR_INVALID_ARG, "x, query_w, keys0 and keys1 are required");
+    if (!t->x || !t->query_w || !t->keys0 || (h->nd > 1 && !t->keys1) || (h->nd > 2 && !t->keys2) || (h->nd > 3 && !t->keys3))
+        return fail(h, PEER_ERR_INVALID_ARG, "x, query_w and one sub-key table per key dimension are required");
     if (need_tables) {
         if (!t->expert_down || !t->expert_up || !t->out)
             return fail(h, PEER_ERR_INVALID_ARG, "expert_down, expert_up and out are required");
@@ -290,6 +347,7 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     q.x = x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
     q.q_ln_out = nullptr; q.q_hat_out = h->use_tc_select ? nullptr : h->q_hat; q.T = n; q.D = c.input_dim; q.H = c.num_heads;
     q.Q = c.query_dim; q.layer_norm = c.layer_norm; q.norm_query = c.norm_query; q.act_dtype = c.act_dtype;
+    if (h->general_select) { q.q_ln_out = h->q_hat; q.q_hat_out = nullptr; }
     cudaEvent_t* ev = nullptr;
     if (h->timing) {
         if (h->tev_used + 4 > h->tev.size()) {
@@ -309,7 +367,18 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         CU_TRY(h, launch_query_simt(q, s));
     if (ev) CU_TRY(h, cudaEventRecord(ev[1], s));
 
-    if (h->use_tc_select) {
+    if (h->general_select) {
+        SelectNdArgs na{};
+        na.q_ln = h->q_hat;
+        const void* kk[4] = {t->keys0, t->keys1, t->keys2, t->keys3};
+        for (int d = 0; d < h->nd; ++d) { na.keys[d] = kk[d]; na.n[d] = h->n[d]; na.kp[d] = h->kp[d]; na.mult[d] = h->mult[d]; }
+        na.nd = h->nd; na.Q = c.query_dim; na.k = c.top_k; na.norm_keys = c.norm_keys; na.norm_query = c.norm_query;
+        na.act_dtype = c.act_dtype; na.rows = n * c.num_heads;
+        na.ids32 = h->sel_ids; na.weights = h->sel_w; na.ids64 = ids_out; na.raw_scores = scores_out;
+        cudaError_t se = launch_select_nd(na, s);
+        if (se == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "selection over this key grid is not implemented");
+        CU_TRY(h, se);
+    } else if (h->use_tc_select) {
         SelectTcArgs ta{};
         ta.q_split = h->q_split; ta.term_rows = c.max_tokens * c.num_heads; ta.keys0 = t->keys0; ta.keys1 = t->keys1;
         ta.invn0 = h->invn0; ta.invn1 = h->invn1; ta.rows = n * c.num_heads; ta.Q = c.query_dim;
@@ -338,8 +407,8 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     g.down_scale = t->down_scale; g.up_scale = t->up_scale; g.out = out; g.T = n;
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
-    g.status = h->status; g.sm_count = h->sm_count;
-    cudaError_t e = launch_gather_eval(g, s);
+    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden;
+    cudaError_t e = h->hidden > 1 ? launch_gather_hidden(g, s) : launch_gather_eval(g, s);
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
                     c.input_dim, c.output_dim, g.HK);
@@ -380,7 +449,7 @@ extern "C" int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_
     if (rc) return rc;
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = normalise_keys(h, t->keys0, t->keys1, s);
+    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, s);
     if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
     if (rc) return rc;
     const int ab = act_bytes(c.act_dtype);
@@ -441,7 +510,7 @@ extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64
     dt.x = h->d_x[0]; dt.out = h->d_out[0];
     rc = check_tensors(h, &dt, true);
     if (rc) return rc;
-    rc = normalise_keys(h, t->keys0, t->keys1, h->st_run);
+    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, h->st_run);
     if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, h->st_run);
     if (rc) return rc;
 
@@ -505,6 +574,8 @@ extern "C" int peer_select(peer_handle_t h, const float* queries, const void* ke
     if (!h) return PEER_ERR_INVALID_ARG;
     if (n_tokens == 0) return PEER_OK;
     if (!queries || !keys0 || !keys1) return fail(h, PEER_ERR_INVALID_ARG, "queries and keys are required");
+    if (h->general_select)
+        return fail(h, PEER_ERR_UNSUPPORTED, "peer_select takes two sub-key tables; this layer has %d key dimensions: use peer_select_nd", h->nd);
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = normalise_keys(h, keys0, keys1, s);
@@ -520,6 +591,28 @@ extern "C" int peer_select(peer_handle_t h, const float* queries, const void* ke
         CU_TRY(h, launch_select_simt(sa, s));
         h->launches += 2;
     }
+    return PEER_OK;
+}
+
+extern "C" int peer_select_nd(peer_handle_t h, const float* queries, const void* const* keys, int64_t n_tokens,
+                              int64_t* ids_out, float* scores_out, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    if (!queries || !keys) return fail(h, PEER_ERR_INVALID_ARG, "queries and keys are required");
+    const peer_config_t& c = h->cfg;
+    SelectNdArgs na{};
+    na.q_ln = queries;
+    for (int d = 0; d < h->nd; ++d) {
+        if (!keys[d]) return fail(h, PEER_ERR_INVALID_ARG, "sub-key table %d is null", d);
+        na.keys[d] = keys[d]; na.n[d] = h->n[d]; na.kp[d] = h->kp[d]; na.mult[d] = h->mult[d];
+    }
+    na.nd = h->nd; na.Q = c.query_dim; na.k = c.top_k; na.norm_keys = c.norm_keys; na.norm_query = c.norm_query;
+    na.act_dtype = c.act_dtype; na.rows = n_tokens * c.num_heads;
+    na.ids64 = ids_out; na.raw_scores = scores_out;
+    cudaError_t e = launch_select_nd(na, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "selection over this key grid is not implemented");
+    CU_TRY(h, e);
+    h->launches += 1;
     return PEER_OK;
 }
 
@@ -540,8 +633,9 @@ extern "C" int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* i
     g.down_scale = down_scale; g.up_scale = up_scale; g.out = out; g.T = n_tokens;
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
-    g.status = h->status; g.sm_count = h->sm_count;
-    cudaError_t e = launch_gather_eval(g, static_cast<cudaStream_t>(stream));
+    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden;
+    cudaError_t e = h->hidden > 1 ? launch_gather_hidden(g, static_cast<cudaStream_t>(stream))
+                                  : launch_gather_eval(g, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
                     c.input_dim, c.output_dim, g.HK);
@@ -559,6 +653,8 @@ extern "C" int peer_gather_eval_partial(peer_handle_t h, const void* x, const in
     const peer_config_t& c = h->cfg;
     if (!x || !ids || !weights || !counts || !expert_down || !expert_up || !out_f32)
         return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_partial: null pointer");
+    if (h->hidden > 1)
+        return fail(h, PEER_ERR_UNSUPPORTED, "peer_gather_eval_partial: experts with several neurons are not implemented");
     if (entries_per_token <= 0 || n_local_rows <= 0 || n_local_rows > c.num_experts)
         return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_partial: entries_per_token and n_local_rows must be positive, rows <= num_experts");
     if (c.table_dtype == PEER_DTYPE_E4M3 && (!down_scale || !up_scale))
@@ -599,8 +695,9 @@ extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const v
     g.d_down = grad_down; g.d_up = grad_up; g.dx = grad_x; g.dweights = grad_weights;
     g.T = n_tokens; g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
-    g.status = h->status; g.sm_count = h->sm_count;
-    cudaError_t e = launch_gather_grad(g, static_cast<cudaStream_t>(stream));
+    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden;
+    cudaError_t e = h->hidden > 1 ? launch_gather_hidden_grad(g, static_cast<cudaStream_t>(stream))
+                                  : launch_gather_grad(g, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert backward: row width %d/%d is not implemented for this dtype (bf16 up to 2048, fp32 up to 1024)",
                     c.input_dim, c.output_dim);

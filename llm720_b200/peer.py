@@ -42,8 +42,8 @@ class PeerOp:
                  activation: str = "gelu", norm_keys: bool = True, norm_query: bool = True,
                  layer_norm: bool = True, index_mode: str = "reference", max_tokens: int = 16384,
                  expert_hidden_size: int = 1, device=None):
-        if len(product_key_dim) != 2:
-            raise ValueError(f"product_key_dim={list(product_key_dim)}: only two key dimensions are implemented")
+        if not 1 <= len(product_key_dim) <= 4:
+            raise ValueError(f"product_key_dim={list(product_key_dim)}: one to four key dimensions are implemented")
         if activation not in ("gelu", "relu"):
             raise ValueError(f"Unsupported activation: {activation}")
         if index_mode not in ("reference", "product"):
@@ -56,15 +56,19 @@ class PeerOp:
         self.lib = _lib.load()
         cfg = _lib.PeerConfig(
             abi_version=_lib.ABI_VERSION, input_dim=input_dim, output_dim=output_dim,
-            num_experts=int(product_key_dim[0]) * int(product_key_dim[1]), top_k=top_k,
+            num_experts=math.prod(int(n) for n in product_key_dim), top_k=top_k,
             num_heads=num_heads, query_dim=query_dim, n_keys0=int(product_key_dim[0]),
-            n_keys1=int(product_key_dim[1]), expert_hidden_size=expert_hidden_size,
+            n_keys1=int(product_key_dim[1]) if len(product_key_dim) > 1 else 1,
+            n_keys2=int(product_key_dim[2]) if len(product_key_dim) > 2 else 1,
+            n_keys3=int(product_key_dim[3]) if len(product_key_dim) > 3 else 1,
+            num_key_dims=len(product_key_dim), expert_hidden_size=expert_hidden_size,
             activation=_lib.ACT_GELU if activation == "gelu" else _lib.ACT_RELU,
             norm_keys=int(norm_keys), norm_query=int(norm_query), layer_norm=int(layer_norm),
             act_dtype=_DT[act_dtype], table_dtype=_DT[table_dtype],
             index_mode=_lib.INDEX_REFERENCE if index_mode == "reference" else _lib.INDEX_PRODUCT,
             max_tokens=int(max_tokens))
         self.cfg = cfg
+        self.num_key_dims = len(product_key_dim)
         self.act_dtype, self.table_dtype = act_dtype, table_dtype
         self.handle = C.c_void_p()
         with torch.cuda.device(self.device):
@@ -103,7 +107,7 @@ class PeerOp:
         a, tb = self.act_dtype, self.table_dtype
         self._dev(x, "x", a, host_ok=host_io)
         self._dev(out, "out", a, host_ok=host_io)
-        for k in ("query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1"):
+        for k in ("query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1", "keys2", "keys3"):
             self._dev(w.get(k), k, a)
         for k in ("expert_down", "expert_up"):
             self._dev(w.get(k), k, tb)
@@ -114,7 +118,9 @@ class PeerOp:
             query_b=None if w.get("query_b") is None else w["query_b"].data_ptr(),
             ln_w=None if w.get("ln_w") is None else w["ln_w"].data_ptr(),
             ln_b=None if w.get("ln_b") is None else w["ln_b"].data_ptr(),
-            keys0=w["keys0"].data_ptr(), keys1=w["keys1"].data_ptr(),
+            keys0=w["keys0"].data_ptr(), keys1=None if w.get("keys1") is None else w["keys1"].data_ptr(),
+            keys2=None if w.get("keys2") is None else w["keys2"].data_ptr(),
+            keys3=None if w.get("keys3") is None else w["keys3"].data_ptr(),
             expert_down=None if w.get("expert_down") is None else w["expert_down"].data_ptr(),
             expert_up=None if w.get("expert_up") is None else w["expert_up"].data_ptr(),
             down_scale=None if w.get("down_scale") is None else w["down_scale"].data_ptr(),
@@ -161,6 +167,23 @@ class PeerOp:
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_select(self.handle, _ptr(queries), _ptr(keys0), _ptr(keys1), T,
                                              _ptr(ids), _ptr(sc), _stream(self.device)))
+        return ids, sc
+
+    def select_nd(self, queries: torch.Tensor, keys) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Selection over a key grid of any dimensionality: queries fp32 [T, H, Q] (after LayerNorm), keys a
+        sequence of num_key_dims tables -> (ids int64, raw scores fp32) [T, H, k]."""
+        self._dev(queries, "queries", torch.float32)
+        if len(keys) != self.num_key_dims:
+            raise ValueError(f"{len(keys)} sub-key tables for {self.num_key_dims} key dimensions")
+        for i, kt in enumerate(keys):
+            self._dev(kt, f"keys{i}", self.act_dtype)
+        T = queries.shape[0]
+        ids = torch.empty(T, self.cfg.num_heads, self.cfg.top_k, dtype=torch.int64, device=self.device)
+        sc = torch.empty(T, self.cfg.num_heads, self.cfg.top_k, dtype=torch.float32, device=self.device)
+        ptrs = (C.c_void_p * 4)(*[kt.data_ptr() for kt in keys])
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_select_nd(self.handle, _ptr(queries), ptrs, T, _ptr(ids), _ptr(sc),
+                                                _stream(self.device)))
         return ids, sc
 
     def gather_eval(self, x, ids32, weights, down, up, down_scale=None, up_scale=None, out=None):
@@ -290,10 +313,12 @@ class PEER(nn.Module):
                                  f"must equal the number of experts {num_experts}")
         if activation not in ("relu", "gelu"):
             raise ValueError(f"Unsupported activation: {activation}")
-        if len(self.product_key_dim) != 2:
-            raise ValueError("peer_b200 implements two-dimensional product keys only")
-        if expert_hidden_size != 1:
-            raise ValueError("peer_b200 implements single-neuron experts (expert_hidden_size=1) only")
+        if not 1 <= len(self.product_key_dim) <= 4:
+            raise ValueError("peer_b200 implements product keys of one to four dimensions")
+        if not 1 <= expert_hidden_size <= 16:
+            raise ValueError("peer_b200 implements experts of 1 to 16 hidden neurons")
+        if query_dim % len(self.product_key_dim):
+            raise ValueError(f"query_dim {query_dim} must be divisible by the {len(self.product_key_dim)} key dimensions")
 
         self.query_proj = nn.Linear(input_dim, num_heads * query_dim)
         self.query_layer_norm = nn.LayerNorm(query_dim) if batch_norm_query else None
@@ -333,9 +358,10 @@ class PEER(nn.Module):
     # -- operator management -------------------------------------------------
     def _weights(self) -> dict:
         ln = self.query_layer_norm
+        keys = {f"keys{i}": k for i, k in enumerate(self.sub_keys)}
         return dict(query_w=self.query_proj.weight, query_b=self.query_proj.bias,
                     ln_w=None if ln is None else ln.weight, ln_b=None if ln is None else ln.bias,
-                    keys0=self.sub_keys[0], keys1=self.sub_keys[1], expert_down=self.expert_down.weight,
+                    **keys, expert_down=self.expert_down.weight,
                     expert_up=self.expert_up.weight, down_scale=self.expert_down_scale,
                     up_scale=self.expert_up_scale)
 
@@ -343,7 +369,7 @@ class PEER(nn.Module):
         cap = min(max(n_tokens, 1), self.max_slice_tokens)
         table_dtype = self.expert_down.weight.dtype
         key = (str(device), act_dtype, table_dtype, self.index_mode, self.activation_name,
-               self.norm_keys, self.norm_query, self.batch_norm_query)
+               self.norm_keys, self.norm_query, self.batch_norm_query, self.expert_hidden_size)
         if self._op is None or self._op_key != key or self._op.cfg.max_tokens < cap:
             if self._op is not None:
                 cap = max(cap, self._op.cfg.max_tokens) if self._op_key == key else cap
@@ -354,7 +380,8 @@ class PEER(nn.Module):
                               top_k=self.num_experts_per_tok, act_dtype=act_dtype, table_dtype=table_dtype,
                               activation=self.activation_name, norm_keys=self.norm_keys,
                               norm_query=self.norm_query, layer_norm=self.batch_norm_query,
-                              index_mode=self.index_mode, max_tokens=cap, device=device)
+                              index_mode=self.index_mode, max_tokens=cap,
+                              expert_hidden_size=self.expert_hidden_size, device=device)
             self._op_key = key
         return self._op
 
@@ -371,7 +398,8 @@ class PEER(nn.Module):
                                   top_k=self.num_experts_per_tok, act_dtype=act_dtype, table_dtype=act_dtype,
                                   activation=self.activation_name, norm_keys=self.norm_keys,
                                   norm_query=self.norm_query, layer_norm=self.batch_norm_query,
-                                  index_mode="product", max_tokens=cap, device=device)
+                                  index_mode="product", max_tokens=cap,
+                                  expert_hidden_size=self.expert_hidden_size, device=device)
             self._sel_op_key = key
         return self._sel_op
 
@@ -455,7 +483,11 @@ class PEER(nn.Module):
             raise ValueError("top_k must equal num_experts_per_tok")
         B, S, H, Q = queries.shape
         op = self._operator(queries.device, self.sub_keys[0].dtype, B * S)
-        ids, sc = op.select(queries.float().contiguous().view(B * S, H, Q), self.sub_keys[0], self.sub_keys[1])
+        q = queries.float().contiguous().view(B * S, H, Q)
+        if len(self.sub_keys) == 2:
+            ids, sc = op.select(q, self.sub_keys[0], self.sub_keys[1])
+        else:
+            ids, sc = op.select_nd(q, [k.detach() for k in self.sub_keys])
         return ids.view(B, S, H, -1), sc.view(B, S, H, -1).to(queries.dtype)
 
     _get_expert_indices = select

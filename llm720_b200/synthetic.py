@@ -9,6 +9,7 @@ whole table.
 """
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass, replace
 from typing import Dict, Optional, Tuple
 
@@ -24,16 +25,18 @@ class PeerConfig:
     output_dim: int
     num_heads: int
     query_dim: int
-    product_key_dim: Tuple[int, int]
+    product_key_dim: Tuple[int, ...]
     top_k: int
     dtype: torch.dtype            # activations and small weights
     table_dtype: torch.dtype      # expert_down / expert_up storage
     batch: int
     seq: int
+    expert_hidden_size: int = 1
+    batch_norm_query: bool = True
 
     @property
     def num_experts(self) -> int:
-        return self.product_key_dim[0] * self.product_key_dim[1]
+        return math.prod(self.product_key_dim)
 
     @property
     def tokens(self) -> int:
@@ -42,9 +45,9 @@ class PeerConfig:
     def module_kwargs(self) -> dict:
         return dict(input_dim=self.input_dim, output_dim=self.output_dim,
                     num_experts=self.num_experts, num_experts_per_tok=self.top_k,
-                    num_heads=self.num_heads, expert_hidden_size=1, query_dim=self.query_dim,
+                    num_heads=self.num_heads, expert_hidden_size=self.expert_hidden_size, query_dim=self.query_dim,
                     product_key_dim=list(self.product_key_dim), activation="gelu", dropout=0.0,
-                    norm_keys=True, norm_query=True, batch_norm_query=True)
+                    norm_keys=True, norm_query=True, batch_norm_query=self.batch_norm_query)
 
     def gathered_bytes_per_token(self) -> int:
         """Algorithmic bytes the expert stage must fetch for one token: one
@@ -53,7 +56,7 @@ class PeerConfig:
         b = torch.empty(0, dtype=self.table_dtype).element_size()
         per_row_extra = 4 if self.table_dtype == torch.float8_e4m3fn else 0
         return self.num_heads * self.top_k * (
-            self.input_dim * b + self.output_dim * b + 2 * per_row_extra)
+            (self.input_dim * b + self.output_dim * b) * self.expert_hidden_size + 2 * per_row_extra)
 
 
 CONFIGS: Dict[str, PeerConfig] = {
@@ -105,27 +108,29 @@ def make_weights(cfg: PeerConfig, seed: int = 0, device="cpu", table_rows: Optio
     ``table_rows`` limits the tables to their first rows (enough for the
     reference's index mode, whose ids stay below n0+n1-1)."""
     D, Do, H, Q = cfg.input_dim, cfg.output_dim, cfg.num_heads, cfg.query_dim
-    n0, n1 = cfg.product_key_dim
     g = _gen(device, seed)
     rn = lambda *s: torch.randn(*s, generator=g, device=device, dtype=torch.float32)
     sd = {}
     sd["query_proj.weight"] = (rn(H * Q, D) * D ** -0.5).to(cfg.dtype)
     if random_affine:
         sd["query_proj.bias"] = (rn(H * Q) * 0.1).to(cfg.dtype)
-        sd["query_layer_norm.weight"] = (1.0 + 0.2 * rn(Q)).to(cfg.dtype)
-        sd["query_layer_norm.bias"] = (0.1 * rn(Q)).to(cfg.dtype)
+        if cfg.batch_norm_query:
+            sd["query_layer_norm.weight"] = (1.0 + 0.2 * rn(Q)).to(cfg.dtype)
+            sd["query_layer_norm.bias"] = (0.1 * rn(Q)).to(cfg.dtype)
     else:
         sd["query_proj.bias"] = torch.zeros(H * Q, dtype=cfg.dtype, device=device)
-        sd["query_layer_norm.weight"] = torch.ones(Q, dtype=cfg.dtype, device=device)
-        sd["query_layer_norm.bias"] = torch.zeros(Q, dtype=cfg.dtype, device=device)
-    half = Q // 2
-    sd["sub_keys.0"] = (rn(n0, half) * half ** -0.5).to(cfg.dtype)
-    sd["sub_keys.1"] = (rn(n1, half) * half ** -0.5).to(cfg.dtype)
+        if cfg.batch_norm_query:
+            sd["query_layer_norm.weight"] = torch.ones(Q, dtype=cfg.dtype, device=device)
+            sd["query_layer_norm.bias"] = torch.zeros(Q, dtype=cfg.dtype, device=device)
+    width = Q // len(cfg.product_key_dim)
+    for i, n in enumerate(cfg.product_key_dim):
+        sd[f"sub_keys.{i}"] = (rn(n, width) * width ** -0.5).to(cfg.dtype)
     if not tables:
         return sd
     rows = cfg.num_experts if table_rows is None else min(table_rows, cfg.num_experts)
-    sd["expert_down.weight"] = _table(rows, D, D ** -0.5, cfg.table_dtype, device, seed, 1)
-    sd["expert_up.weight"] = _table(rows, Do, D ** -0.5, cfg.table_dtype, device, seed, 2)
+    h = cfg.expert_hidden_size
+    sd["expert_down.weight"] = _table(rows, D * h, D ** -0.5, cfg.table_dtype, device, seed, 1)
+    sd["expert_up.weight"] = _table(rows, Do * h, (D * h) ** -0.5 if h > 1 else D ** -0.5, cfg.table_dtype, device, seed, 2)
     return sd
 
 

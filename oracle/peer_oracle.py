@@ -117,7 +117,9 @@ def select(queries: torch.Tensor, sub_keys: Sequence[torch.Tensor], top_k: int,
     if nd == 1:                                           # experts.py:197-200
         k = min(top_k, top_s[0].shape[-1])
         fs, fi = torch.topk(top_s[0], k=k, dim=-1)
-        return fi, fs
+        # the reference returns the positions inside its candidate list here (0..k-1), not key indices;
+        # "product" mode returns the keys those positions stand for
+        return (torch.gather(top_i[0], -1, fi) if index_mode == "product" else fi), fs
 
     mult = [1] * nd                                       # experts.py:207-210
     for d in range(nd - 2, -1, -1):

@@ -104,3 +104,27 @@ def oracle_gradients(cfg, sd, x, grad_out, index_mode="reference", dtype=torch.f
 def rel_err(a: torch.Tensor, b: torch.Tensor) -> float:
     """Largest absolute difference relative to the largest reference entry."""
     return float((a.double() - b.double()).abs().max() / b.double().abs().max().clamp_min(1e-30))
+
+
+GENERAL_CASES = ["h8_fp32", "k3d_h8_fp32", "k3d_pruned_fp32", "k4d_h2_fp32", "k1d_fp32"]
+
+
+def load_general(name: str):
+    """Golden case written by tests/golden/make_golden_general.py (constructor options beyond the benchmark
+    shape): (cfg, state-dict, x, record)."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden_general", os.path.join(GOLDEN, "make_golden_general.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    cfg, _ = mod.config_of(name)
+    rec = np.load(os.path.join(GOLDEN, name + ".npz"))
+    sd = {k[2:]: torch.from_numpy(rec[k]) for k in rec.files if k.startswith("w:")}
+    return cfg, sd, torch.from_numpy(rec["x"]), rec
+
+
+def general_oracle_weights(sd: dict, cfg) -> orc.PeerWeights:
+    f = lambda k: sd[k].float() if k in sd else None
+    return orc.PeerWeights(f("query_proj.weight"), f("query_proj.bias"), f("query_layer_norm.weight"),
+                           f("query_layer_norm.bias"),
+                           [sd[f"sub_keys.{i}"].float() for i in range(len(cfg.product_key_dim))],
+                           f("expert_down.weight"), f("expert_up.weight"))

@@ -30,11 +30,13 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_layouts_match_header():
-    # peer_config_t: int32 x3, int64, int32 x14 (with natural padding), int64
-    assert C.sizeof(_lib.PeerConfig) == 88
+    # peer_config_t: int32 x3, int64, int32 x14 (with natural padding), int64, int32 x3 (+ tail padding)
+    assert C.sizeof(_lib.PeerConfig) == 104
     assert _lib.PeerConfig.num_experts.offset == 16
     assert _lib.PeerConfig.max_tokens.offset == 80
-    assert C.sizeof(_lib.PeerTensors) == 14 * 8
+    assert _lib.PeerConfig.num_key_dims.offset == 88 and _lib.PeerConfig.n_keys3.offset == 96
+    assert C.sizeof(_lib.PeerTensors) == 16 * 8
+    assert _lib.PeerTensors.keys2.offset == 14 * 8
 
 
 def test_create_rejects_bad_arguments_without_a_device():
@@ -45,11 +47,15 @@ def test_create_rejects_bad_arguments_without_a_device():
     assert lib.peer_create(C.byref(cfg), C.byref(h)) == _lib.ERR_INVALID_ARG
     assert b"abi_version" in lib.peer_last_error(None)
     cfg = _lib.PeerConfig(abi_version=_lib.ABI_VERSION, input_dim=256, output_dim=256, num_experts=16,
-                          top_k=4, num_heads=2, query_dim=32, n_keys0=4, n_keys1=4, expert_hidden_size=2,
+                          top_k=4, num_heads=2, query_dim=32, n_keys0=4, n_keys1=4, expert_hidden_size=17,
                           max_tokens=8)
     assert lib.peer_create(C.byref(cfg), C.byref(h)) == _lib.ERR_UNSUPPORTED
     assert b"expert_hidden_size" in lib.peer_last_error(None)
     cfg.expert_hidden_size = 1
+    cfg.num_key_dims = 5
+    assert lib.peer_create(C.byref(cfg), C.byref(h)) == _lib.ERR_UNSUPPORTED
+    assert b"num_key_dims" in lib.peer_last_error(None)
+    cfg.num_key_dims = 2
     cfg.n_keys1 = 5
     assert lib.peer_create(C.byref(cfg), C.byref(h)) == _lib.ERR_INVALID_ARG
     assert not h.value

@@ -68,9 +68,11 @@ def test_rejects_what_the_kernels_do_not_implement():
     with pytest.raises(ValueError):
         PEER(32, 32, 64, activation="swish", product_key_dim=[8, 8])
     with pytest.raises(ValueError):
-        PEER(32, 32, 64, product_key_dim=[4, 4, 4])
+        PEER(32, 32, 32, product_key_dim=[2, 2, 2, 2, 2])
     with pytest.raises(ValueError):
-        PEER(32, 32, 64, expert_hidden_size=2, product_key_dim=[8, 8])
+        PEER(32, 32, 64, expert_hidden_size=17, product_key_dim=[8, 8])
+    m3 = PEER(32, 32, 64, expert_hidden_size=2, query_dim=30, product_key_dim=[4, 4, 4])
+    assert len(m3.sub_keys) == 3 and m3.sub_keys[0].shape == (4, 10) and m3.expert_up.weight.shape == (64, 64)
 
 
 def test_no_cpu_path():
