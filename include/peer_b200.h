@@ -190,6 +190,13 @@ int peer_select_noalloc(const peer_config_t* cfg, const float* queries, const vo
                         const void* keys1, int64_t n_tokens, int64_t* ids_out, float* scores_out,
                         void* stream);
 
+/* Expert-usage histogram on the device: counts[id] += 1 for every id in ids[0 .. n_ids) (int64, the
+ * layout of ids_out / the module's _last_expert_indices).  Replaces the host loop of
+ * ExpertUsageTracker.record_usage (llm/utils/experts/tracking.py:96-100).  No handle; ids outside
+ * [0, num_experts) are not counted but added to *dropped when that pointer is given.  Asynchronous. */
+int peer_usage_histogram(const int64_t* ids, int64_t n_ids, int64_t* counts, int64_t num_experts,
+                         int64_t* dropped, void* stream);
+
 /* Reads and clears the device status word (synchronises `stream`).  Returns
  * PEER_OK, PEER_ERR_DEVICE_TIMEOUT or PEER_ERR_BOUNDS.  The kernels never
  * trap: a bounded wait that runs out, or an expert id outside the table,
