@@ -110,6 +110,15 @@ const char* peer_last_error(peer_handle_t h);
  * Asynchronous on `stream` (a cudaStream_t). */
 int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, void* stream);
 
+/* The feed-forward half of the reference's TransformerBlock.forward (llm/models/foundation.py:
+ * 196-205) in one call: out = hidden + PEER(LayerNorm(hidden)), with t->x = hidden [T, input_dim]
+ * (act_dtype) and the block's ln_2 parameters ln_w, ln_b (fp32 [input_dim], either may be NULL) and
+ * eps.  The normalised rows go to library scratch (allocated on the first call), the residual is
+ * added where the expert stage writes its result.  input_dim must equal output_dim; t->out may not
+ * alias t->x.  Asynchronous on `stream`. */
+int peer_block_forward(peer_handle_t h, const peer_tensors_t* t, const float* ln_w, const float* ln_b,
+                       float ln_eps, int64_t n_tokens, void* stream);
+
 /* Same, with t->x and t->out (and the optional ids/scores outputs) in HOST
  * memory (pinned for full speed): token slices are copied in, processed and
  * copied out on three internal streams so transfers overlap the kernels.

@@ -40,6 +40,8 @@ EXPORTS = {
     "peer_destroy": (C.c_int, [C.c_void_p]),
     "peer_last_error": (C.c_char_p, [C.c_void_p]),
     "peer_forward": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p]),
+    "peer_block_forward": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
+                                     C.c_void_p]),
     "peer_forward_host": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64]),
     "peer_project_queries": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,

@@ -109,6 +109,7 @@ struct GatherParams {
     int nch_u, nch_v;          // 16-byte chunks per down / up row
     const int32_t* counts;     // optional [T]: entries of token t that are in use (<= HK)
     float* out_f32;            // optional [T, Dout] fp32 output instead of `out`
+    const void* residual;      // optional [T, Dout] in the activation dtype, added to the result
 };
 
 template <typename XT, typename TT, int CH>
@@ -281,6 +282,14 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
                         *reinterpret_cast<float4*>(p.out_f32 + t * p.Dout + c * EPC + q) =
                             make_float4(acc[i * EPC + q], acc[i * EPC + q + 1], acc[i * EPC + q + 2], acc[i * EPC + q + 3]);
                 } else {
+                    if (p.residual) {
+                        if constexpr (EPC * sizeof(XT) >= 16) {     // the table chunk covers whole 16-byte pieces of the row
+                            float rsd[EPC];
+                            XIo<XT, EPC>::load(static_cast<const XT*>(p.residual) + t * p.Dout + c * EPC, rsd);
+#pragma unroll
+                            for (int q = 0; q < EPC; ++q) acc[i * EPC + q] += rsd[q];
+                        }
+                    }
                     XIo<XT, EPC>::store(og + t * p.Dout + c * EPC, acc + i * EPC);
                 }
             }
@@ -343,7 +352,7 @@ cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
     p.down_scale = a.down_scale; p.up_scale = a.up_scale; p.out = a.out; p.T = a.T; p.HK = a.HK;
     p.N = a.N; p.D = a.D; p.Dout = a.Dout; p.activation = a.activation; p.status = a.status;
     p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
-    p.counts = a.counts; p.out_f32 = a.out_f32;
+    p.counts = a.counts; p.out_f32 = a.out_f32; p.residual = a.residual;
     const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
     if (a.act_dtype == PEER_DTYPE_F32 && a.table_dtype == PEER_DTYPE_F32)
         return launch_ch<float, float>(a, p, max_ch, s);

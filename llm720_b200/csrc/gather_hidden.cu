@@ -74,7 +74,9 @@ __global__ void __launch_bounds__(THREADS) gather_hidden_kernel(const GatherArgs
             for (int o = lane; o < a.Dout; o += 32) a.out_f32[t * a.Dout + o] = acc[o];
         } else {
             T* og = static_cast<T*>(a.out);
-            for (int o = lane; o < a.Dout; o += 32) og[t * a.Dout + o] = from_f32<T>(acc[o]);
+            const T* rs = static_cast<const T*>(a.residual);
+            for (int o = lane; o < a.Dout; o += 32)
+                og[t * a.Dout + o] = from_f32<T>(acc[o] + (rs ? to_f32<T>(rs[t * a.Dout + o]) : 0.f));
         }
     }
 }

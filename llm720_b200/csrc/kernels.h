@@ -105,6 +105,7 @@ struct GatherArgs {
     int* status;              // device status word
     int sm_count;
     int hidden;               // neurons per expert (rows are [hidden, D] / [Dout, hidden] blocks); 0 or 1 = single
+    const void* residual;     // optional [T, Dout] act dtype: added to the result (out = residual + y)
     const int32_t* counts;    // optional [T]: how many of token t's HK entries are in use
     float* out_f32;           // optional fp32 output [T, Dout] (partial sums of a row-sharded table)
 };
@@ -154,6 +155,10 @@ struct SelectNdArgs {
     float* raw_scores;        // optional [rows, k]
 };
 cudaError_t launch_select_nd(const SelectNdArgs& a, cudaStream_t s);
+
+// LayerNorm over the model dimension, fp32 parameters (block_ln.cu)
+cudaError_t launch_block_ln(const void* x, int act_dtype, int64_t rows, int D, const float* w, const float* b, float eps,
+                            void* out, cudaStream_t s);
 // one-time per-process attribute set-up (dynamic shared memory opt-in)
 cudaError_t gather_eval_setup();
 cudaError_t select_simt_setup();

@@ -38,6 +38,7 @@ struct peer_op {
     float* invn1 = nullptr;       // [n1]
     int32_t* ovf_rows = nullptr;  // [max_tokens*H] rows the tensor-core select leaves to the exact kernel
     int* ovf_count = nullptr;
+    void* x_ln = nullptr;         // [max_tokens, D] act dtype: LayerNorm of the block input (peer_block_forward)
     int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
     float* sel_w = nullptr;       // [max_tokens, H*k]
     uint16_t* pairs = nullptr;
@@ -99,7 +100,7 @@ namespace peer { int candidates_per_dim_2d(int top_k, int dim_size) { return can
 
 static void free_all(peer_op* h) {
     cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->ovf_rows); cudaFree(h->ovf_count); cudaFree(h->sel_ids);
-    cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status);
+    cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status); cudaFree(h->x_ln);
     for (int b = 0; b < 2; ++b) {
         cudaFree(h->d_x[b]); cudaFree(h->d_out[b]); cudaFree(h->d_ids[b]); cudaFree(h->d_sc[b]);
         if (h->ev_in[b]) cudaEventDestroy(h->ev_in[b]);
@@ -341,7 +342,7 @@ static SelectArgs select_args(peer_op* h, int64_t n_tokens) {
 
 // One slice (n <= max_tokens) of the layer, all pointers on the device.
 static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, void* out, int64_t* ids_out,
-                         float* scores_out, int64_t n, cudaStream_t s) {
+                         float* scores_out, int64_t n, cudaStream_t s, const void* residual = nullptr) {
     const peer_config_t& c = h->cfg;
     QueryArgs q{};
     q.x = x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
@@ -407,7 +408,7 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     g.down_scale = t->down_scale; g.up_scale = t->up_scale; g.out = out; g.T = n;
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
-    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden;
+    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.residual = residual;
     cudaError_t e = h->hidden > 1 ? launch_gather_hidden(g, s) : launch_gather_eval(g, s);
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
@@ -493,6 +494,37 @@ static int host_pipeline_setup(peer_op* h, bool want_ids) {
             CU_TRY(h, cudaMalloc(reinterpret_cast<void**>(&h->d_ids[b]), n * sizeof(int64_t)));
             CU_TRY(h, cudaMalloc(reinterpret_cast<void**>(&h->d_sc[b]), n * sizeof(float)));
         }
+    }
+    return PEER_OK;
+}
+
+extern "C" int peer_block_forward(peer_handle_t h, const peer_tensors_t* t, const float* ln_w, const float* ln_b,
+                                  float ln_eps, int64_t n_tokens, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens < 0) return fail(h, PEER_ERR_INVALID_ARG, "negative token count");
+    if (n_tokens == 0) return PEER_OK;
+    int rc = check_tensors(h, t, true);
+    if (rc) return rc;
+    const peer_config_t& c = h->cfg;
+    if (c.input_dim != c.output_dim)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_block_forward adds the input back: input_dim %d must equal output_dim %d",
+                    c.input_dim, c.output_dim);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t ab = static_cast<size_t>(act_bytes(c.act_dtype));
+    if (!h->x_ln) CU_TRY(h, cudaMalloc(&h->x_ln, ab * c.max_tokens * c.input_dim));
+    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, s);
+    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
+    if (rc) return rc;
+    const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += c.max_tokens) {
+        const int64_t n = n_tokens - t0 < c.max_tokens ? n_tokens - t0 : c.max_tokens;
+        const char* xs = static_cast<const char*>(t->x) + t0 * c.input_dim * ab;
+        CU_TRY(h, launch_block_ln(xs, c.act_dtype, n, c.input_dim, ln_w, ln_b, ln_eps, h->x_ln, s));
+        h->launches += 1;
+        rc = forward_slice(h, t, h->x_ln, static_cast<char*>(t->out) + t0 * c.output_dim * ab,
+                           t->ids_out ? t->ids_out + t0 * HK : nullptr, t->scores_out ? t->scores_out + t0 * HK : nullptr,
+                           n, s, xs);
+        if (rc) return rc;
     }
     return PEER_OK;
 }

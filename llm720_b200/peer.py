@@ -137,6 +137,18 @@ class PeerOp:
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_forward(self.handle, C.byref(t), T, _stream(self.device)))
 
+    def block_forward(self, hidden: torch.Tensor, w: dict, ln_w, ln_b, eps: float, out: torch.Tensor,
+                      ids_out=None, scores_out=None):
+        """out = hidden + layer(LayerNorm(hidden)); hidden, out [T, D] on the device; ln_w, ln_b fp32 [D] or None."""
+        self._dev(ln_w, "ln_w", torch.float32)
+        self._dev(ln_b, "ln_b", torch.float32)
+        if out.data_ptr() == hidden.data_ptr():
+            raise ValueError("out may not alias hidden")
+        t = self._tensors(hidden, w, out, ids_out, scores_out)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_block_forward(self.handle, C.byref(t), _ptr(ln_w), _ptr(ln_b), float(eps),
+                                                    hidden.shape[0], _stream(self.device)))
+
     def forward_host(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None):
         """x and out in (pinned) host memory; returns when out is complete."""
         if x.device.type != "cpu" or out.device.type != "cpu":
@@ -442,6 +454,30 @@ class PEER(nn.Module):
             ids = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.int64, device=x.device)
             sc = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.float32, device=x.device)
         op.forward(x, w, out, ids, sc)
+        self._stash(ids, sc, B, S)
+        return out.view(B, S, self.output_dim)
+
+    def block_forward(self, hidden_states: torch.Tensor, ln_2: nn.LayerNorm) -> torch.Tensor:
+        """``hidden_states + self(ln_2(hidden_states))``: the feed-forward half of the reference's
+        TransformerBlock.forward (foundation.py:196-205) in one library call.  Inference only."""
+        if self._needs_grad(hidden_states) or (torch.is_grad_enabled() and any(p.requires_grad for p in ln_2.parameters())):
+            raise RuntimeError("block_forward is an inference path; call it under torch.no_grad()")
+        if self.training and self.dropout.p > 0:
+            raise RuntimeError("block_forward is an inference path: call eval() first (dropout is set)")
+        w, dt = self._prepare(hidden_states)
+        if hidden_states.device.type != "cuda":
+            raise RuntimeError("peer_b200 runs on CUDA devices only (sm_100a); there is no CPU path")
+        B, S, _ = hidden_states.shape
+        T = B * S
+        x = hidden_states.contiguous().view(T, self.input_dim)
+        op = self._operator(x.device, dt, T)
+        out = torch.empty(T, self.output_dim, dtype=dt, device=x.device)
+        ids = sc = None
+        if self.track_indices:
+            ids = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.int64, device=x.device)
+            sc = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.float32, device=x.device)
+        f32 = lambda p: None if p is None else p.detach().float().contiguous()
+        op.block_forward(x, w, f32(ln_2.weight), f32(ln_2.bias), ln_2.eps, out, ids, sc)
         self._stash(ids, sc, B, S)
         return out.view(B, S, self.output_dim)
 
