@@ -367,6 +367,23 @@ class PEER(nn.Module):
             setattr(self, name + "_scale", s)
         return self
 
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        """A checkpoint written from a module with FP8 tables (``state_dict()`` then holds float8 payloads and the
+        two per-row scale buffers; the reference saves ``model.state_dict()`` with safetensors,
+        llm/training/train.py:201-246) loads into a freshly constructed module: the tables switch to FP8 storage
+        before the tensors are copied."""
+        names = ("expert_down", "expert_up")
+        if all(prefix + n + "_scale" in state_dict for n in names):
+            for n in names:
+                src, scale = state_dict[prefix + n + ".weight"], state_dict[prefix + n + "_scale"]
+                if src.dtype != torch.float8_e4m3fn:
+                    raise TypeError(f"{prefix}{n}.weight comes with a row scale but is {src.dtype}, not float8_e4m3fn")
+                emb = getattr(self, n)
+                dev = emb.weight.device
+                emb.weight = nn.Parameter(torch.empty(src.shape, dtype=src.dtype, device=dev), requires_grad=False)
+                setattr(self, n + "_scale", torch.empty(scale.shape, dtype=scale.dtype, device=dev))
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
     # -- operator management -------------------------------------------------
     def _weights(self) -> dict:
         ln = self.query_layer_norm

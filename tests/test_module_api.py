@@ -104,3 +104,30 @@ def test_fp8_table_quantisation_keeps_module_consistent():
     assert m.expert_down.weight.dtype == torch.float8_e4m3fn
     assert m.expert_down_scale.shape == (64,) and m.expert_up_scale.dtype == torch.float32
     assert "expert_down_scale" in m.state_dict()
+
+
+def test_checkpoint_round_trip_with_fp8_tables(tmp_path):
+    """state_dict -> safetensors file -> fresh module (the reference's save_checkpoint / load_checkpoint,
+    llm/training/train.py:201-262), with quantised tables and their scales."""
+    from safetensors.torch import load_file, save_file
+    torch.manual_seed(0)
+    m = small().bfloat16()
+    m.quantize_tables_e4m3()
+    sd = m.state_dict()
+    assert sd["expert_down.weight"].dtype == torch.float8_e4m3fn and "expert_up_scale" in sd
+    path = str(tmp_path / "layer.safetensors")
+    save_file({k: v.contiguous() for k, v in sd.items()}, path)
+    fresh = small().bfloat16()
+    res = fresh.load_state_dict(load_file(path))
+    assert not res.missing_keys and not res.unexpected_keys
+    for k, v in sd.items():
+        got = fresh.state_dict()[k]
+        assert got.dtype == v.dtype and torch.equal(got.view(torch.uint8), v.view(torch.uint8)), k
+    assert not fresh.expert_down.weight.requires_grad
+    # an unquantised checkpoint still loads into an unquantised module
+    plain = small().bfloat16()
+    path2 = str(tmp_path / "plain.safetensors")
+    save_file(plain.state_dict(), path2)
+    again = small().bfloat16()
+    again.load_state_dict(load_file(path2))
+    assert again.expert_down.weight.dtype == torch.bfloat16 and again.expert_down_scale is None
