@@ -22,15 +22,21 @@ namespace peer {
 
 namespace {
 
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
-constexpr int RING_BYTES_PER_WARP = 24 * 1024;
 constexpr int MAX_STAGES = 12;
 constexpr int MAX_SMEM = 227 * 1024;
 
-template <int CH> struct RingCfg {
+// Warps per CTA (one CTA per SM) and ring bytes per warp.  Rows of a 16-bit or 32-bit table keep the memory
+// system busy with 8 warps; FP8 rows carry half the bytes per decoded element, so that instance is bound by
+// instruction issue and runs 12 warps with smaller rings and packed activations.
+template <typename TT, int CH> struct WarpCfg {
+    static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 12 warps
+    static constexpr int WARPS = MANY ? 12 : 8;
+    static constexpr int RING_BYTES = MANY ? 16 * 1024 : 24 * 1024;
+};
+
+template <typename TT, int CH> struct RingCfg {
     static constexpr int SLOT = CH * 512;   // bytes: one row of up to CH 16-byte chunks per lane
-    static constexpr int ST0 = RING_BYTES_PER_WARP / SLOT;
+    static constexpr int ST0 = WarpCfg<TT, CH>::RING_BYTES / SLOT;
     static constexpr int STAGES = ST0 > MAX_STAGES ? MAX_STAGES : (ST0 < 2 ? 2 : ST0);
 };
 
@@ -113,8 +119,9 @@ struct GatherParams {
 };
 
 template <typename XT, typename TT, int CH>
-__global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherParams p) {
-    using RC = RingCfg<CH>;
+__global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_kernel(const GatherParams p) {
+    using RC = RingCfg<TT, CH>;
+    constexpr int WARPS = WarpCfg<TT, CH>::WARPS;
     constexpr int STAGES = RC::STAGES;
     constexpr int SLOT = RC::SLOT;
     constexpr int EPC = Chunk<TT>::N;            // elements per 16-byte chunk
@@ -166,7 +173,7 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
         }
         // The activation row stays in registers for the whole token: fp32, or (rows longer than 64
         // elements per lane, bf16 activations) as packed bf16 pairs widened at each use.
-        constexpr bool PACKX = (CH * EPC > 64);
+        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH>::MANY && sizeof(XT) == 2);
         static_assert(!PACKX || sizeof(XT) == 2, "long rows need bf16 activations");
         float xr[PACKX ? 1 : CH * EPC];
         uint32_t xp[PACKX ? CH * EPC / 2 : 1];
@@ -299,7 +306,8 @@ __global__ void __launch_bounds__(THREADS, 1) gather_eval_kernel(const GatherPar
 
 template <typename XT, typename TT, int CH>
 size_t smem_bytes(int HK) {
-    using RC = RingCfg<CH>;
+    using RC = RingCfg<TT, CH>;
+    constexpr int WARPS = WarpCfg<TT, CH>::WARPS;
     return static_cast<size_t>(WARPS) * RC::STAGES * RC::SLOT + WARPS * RC::STAGES * 8 +
            static_cast<size_t>(WARPS) * HK * (sizeof(TT) == 1 ? 16 : 8);
 }
@@ -318,9 +326,10 @@ cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
+    constexpr int WARPS = WarpCfg<TT, CH>::WARPS;
     int64_t ctas = (a.T + WARPS - 1) / WARPS;
     if (ctas > a.sm_count) ctas = a.sm_count;
-    gather_eval_kernel<XT, TT, CH><<<static_cast<unsigned>(ctas), THREADS, smem, s>>>(p);
+    gather_eval_kernel<XT, TT, CH><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(p);
     return cudaGetLastError();
 }
 
