@@ -297,25 +297,42 @@ def main():
     e2e = None
     if not args.no_e2e:
         xh = x.cpu().pin_memory()
-        outh = torch.empty(cfg.batch, cfg.seq, cfg.output_dim, dtype=cfg.dtype, pin_memory=True)
+        outs = [torch.empty(cfg.batch, cfg.seq, cfg.output_dim, dtype=cfg.dtype, pin_memory=True) for _ in range(2)]
+        outh = outs[0]
         layer.track_indices = False
         with torch.no_grad():
             for _ in range(3):
                 layer.forward_host(xh, outh)
+            # (1) one blocking call per step
             barrier()
             t0 = time.perf_counter()
             for _ in range(args.steps):
                 layer.forward_host(xh, outh)     # returns when the output has landed on the host
             torch.cuda.synchronize()
+            dt_serial = time.perf_counter() - t0
+            # (2) the same work with step i+1 submitted before step i is waited for (two output buffers):
+            #     every step still copies its input in and its whole output back inside the timed region
+            barrier()
+            t0 = time.perf_counter()
+            prev = None
+            for i in range(args.steps):
+                _, tk = layer.forward_host_async(xh, outs[i & 1])
+                if prev is not None:
+                    layer.forward_host_wait(prev)
+                prev = tk
+            layer.forward_host_wait(prev)
+            torch.cuda.synchronize()
             dt = time.perf_counter() - t0
         layer.track_indices = True
-        t_e = torch.tensor([dt], device=dev, dtype=torch.float64)
+        t_e = torch.tensor([dt, dt_serial], device=dev, dtype=torch.float64)
         if dist is not None:
             dist.all_reduce(t_e, op=dist.ReduceOp.MAX)
-        e2e = {"value": world * T * args.steps / float(t_e.item()), "unit": UNIT,
+        e2e = {"value": world * T * args.steps / float(t_e[0].item()), "unit": UNIT,
                "h2d_bytes_per_step": xh.numel() * xh.element_size() * world,
                "d2h_bytes_per_step": outh.numel() * outh.element_size() * world,
-               "api": "PEER.forward_host -> peer_forward_host (C ABI), pinned host buffers"}
+               "api": "PEER.forward_host_async/_wait -> peer_forward_host_async/_wait (C ABI), pinned host buffers, "
+                      "one step in flight behind the one being waited for",
+               "blocking_call_value": world * T * args.steps / float(t_e[1].item())}
     backward = None
     if args.backward and cfg.table_dtype != torch.float8_e4m3fn:
         backward = time_backward(layer, cfg, x, min(args.steps, 5))

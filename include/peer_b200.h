@@ -129,6 +129,15 @@ int peer_block_forward(peer_handle_t h, const peer_tensors_t* t, const float* ln
  * (llm/models/kernels/peer_cutlass.py:135-234). */
 int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens);
 
+/* The same call split in two, so that consecutive batches overlap: _async enqueues the copies and
+ * kernels of one batch and returns a ticket; _wait blocks until that batch's outputs are complete in
+ * host memory.  t->x must stay unchanged and t->out untouched until the wait; a later batch may be
+ * submitted before an earlier one is waited for (its first copy-in then overlaps the earlier batch's
+ * last copy-out), each with its own output buffer.  Tickets are waited in any order; at most 8 may be
+ * outstanding. */
+int peer_forward_host_async(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, int64_t* ticket);
+int peer_forward_host_wait(peer_handle_t h, int64_t ticket);
+
 /* Stage entry points (used by the parity tests and by callers that need one
  * stage only). */
 

@@ -43,6 +43,8 @@ EXPORTS = {
     "peer_block_forward": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
                                      C.c_void_p]),
     "peer_forward_host": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64]),
+    "peer_forward_host_async": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.POINTER(C.c_int64)]),
+    "peer_forward_host_wait": (C.c_int, [C.c_void_p, C.c_int64]),
     "peer_project_queries": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                               C.c_void_p, C.c_void_p]),

@@ -51,6 +51,9 @@ struct peer_op {
     void* d_out[2] = {nullptr, nullptr};
     int64_t* d_ids[2] = {nullptr, nullptr};
     float* d_sc[2] = {nullptr, nullptr};
+    int64_t host_slices = 0;      // slices submitted so far by the host-buffer path (staging buffers alternate)
+    int64_t host_calls = 0;       // calls submitted so far: the ticket of the next call
+    cudaEvent_t ev_call[8] = {};  // completion of the last 8 calls (recorded after their last copy-out)
     int64_t launches = 0;
     // optional per-stage timing (peer_stage_timing): events recorded around each stage launch
     bool timing = false;
@@ -107,6 +110,7 @@ static void free_all(peer_op* h) {
         if (h->ev_run[b]) cudaEventDestroy(h->ev_run[b]);
         if (h->ev_out[b]) cudaEventDestroy(h->ev_out[b]);
     }
+    for (int i = 0; i < 8; ++i) if (h->ev_call[i]) cudaEventDestroy(h->ev_call[i]);
     for (cudaEvent_t e : h->tev) cudaEventDestroy(e);
     h->tev.clear();
     if (h->st_in) cudaStreamDestroy(h->st_in);
@@ -473,9 +477,13 @@ static int host_pipeline_setup(peer_op* h, bool want_ids) {
         // scratch: measured best on B200 (1,184: 2.50 M tokens/s end to end; 2,368: 3.27 M; 4,736: 3.56 M;
         // 8,192: 3.15 M) - every slice costs about 0.2 ms of launch gaps and partial waves, while long
         // slices delay the first kernel and the last copy-out.
+        // That holds for a call that blocks until its output is complete.  Batches submitted ahead of one another
+        // (peer_forward_host_async) hide the first copy-in and the last copy-out behind their neighbours' kernels,
+        // so they run as one slice of up to max_tokens; the staging buffers are sized for that.
         int64_t chunk = static_cast<int64_t>(h->sm_count) * 8 * 4;
         if (chunk > c.max_tokens) chunk = c.max_tokens;
         h->host_chunk = chunk;
+        chunk = c.max_tokens;
         CU_TRY(h, cudaStreamCreateWithFlags(&h->st_in, cudaStreamNonBlocking));
         CU_TRY(h, cudaStreamCreateWithFlags(&h->st_run, cudaStreamNonBlocking));
         CU_TRY(h, cudaStreamCreateWithFlags(&h->st_out, cudaStreamNonBlocking));
@@ -489,7 +497,7 @@ static int host_pipeline_setup(peer_op* h, bool want_ids) {
         }
     }
     if (want_ids && !h->d_ids[0]) {
-        const size_t n = static_cast<size_t>(h->host_chunk) * c.num_heads * c.top_k;
+        const size_t n = static_cast<size_t>(c.max_tokens) * c.num_heads * c.top_k;
         for (int b = 0; b < 2; ++b) {
             CU_TRY(h, cudaMalloc(reinterpret_cast<void**>(&h->d_ids[b]), n * sizeof(int64_t)));
             CU_TRY(h, cudaMalloc(reinterpret_cast<void**>(&h->d_sc[b]), n * sizeof(float)));
@@ -529,10 +537,9 @@ extern "C" int peer_block_forward(peer_handle_t h, const peer_tensors_t* t, cons
     return PEER_OK;
 }
 
-extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens) {
+static int host_submit(peer_op* h, const peer_tensors_t* t, int64_t n_tokens, int64_t* ticket, bool blocking) {
     if (!h) return PEER_ERR_INVALID_ARG;
     if (n_tokens < 0) return fail(h, PEER_ERR_INVALID_ARG, "negative token count");
-    if (n_tokens == 0) return PEER_OK;
     if (!t || !t->x || !t->out) return fail(h, PEER_ERR_INVALID_ARG, "x and out are required");
     const peer_config_t& c = h->cfg;
     const bool want_ids = t->ids_out || t->scores_out;
@@ -548,9 +555,9 @@ extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64
 
     const int ab = act_bytes(c.act_dtype);
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
-    const int64_t chunk = h->host_chunk;
-    int64_t i = 0;
-    for (int64_t t0 = 0; t0 < n_tokens; t0 += chunk, ++i) {
+    const int64_t chunk = blocking ? h->host_chunk : c.max_tokens;
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += chunk, ++h->host_slices) {
+        const int64_t i = h->host_slices;          // counts across calls: a call may start while the previous one drains
         const int b = static_cast<int>(i & 1);
         const int64_t n = n_tokens - t0 < chunk ? n_tokens - t0 : chunk;
         // x staging buffer b is free once the kernels of slice i-2 are done
@@ -576,9 +583,34 @@ extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64
                                       cudaMemcpyDeviceToHost, h->st_out));
         CU_TRY(h, cudaEventRecord(h->ev_out[b], h->st_out));
     }
-    CU_TRY(h, cudaStreamSynchronize(h->st_out));
-    CU_TRY(h, cudaStreamSynchronize(h->st_run));
+    cudaEvent_t& done = h->ev_call[h->host_calls & 7];
+    if (!done) CU_TRY(h, cudaEventCreateWithFlags(&done, cudaEventDisableTiming));
+    CU_TRY(h, cudaEventRecord(done, h->st_out));
+    if (ticket) *ticket = h->host_calls;
+    ++h->host_calls;
     return PEER_OK;
+}
+
+extern "C" int peer_forward_host_wait(peer_handle_t h, int64_t ticket) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (ticket < 0 || ticket >= h->host_calls) return fail(h, PEER_ERR_INVALID_ARG, "no such call: ticket %lld", static_cast<long long>(ticket));
+    if (ticket + 8 <= h->host_calls) {             // its event has been reused: everything up to now covers it
+        CU_TRY(h, cudaStreamSynchronize(h->st_out));
+        return PEER_OK;
+    }
+    CU_TRY(h, cudaEventSynchronize(h->ev_call[ticket & 7]));
+    return PEER_OK;
+}
+
+extern "C" int peer_forward_host_async(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, int64_t* ticket) {
+    return host_submit(h, t, n_tokens, ticket, false);
+}
+
+extern "C" int peer_forward_host(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens) {
+    int64_t ticket = 0;
+    const int rc = host_submit(h, t, n_tokens, &ticket, true);
+    if (rc) return rc;
+    return peer_forward_host_wait(h, ticket);
 }
 
 extern "C" int peer_project_queries(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens,

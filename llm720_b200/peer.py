@@ -160,6 +160,22 @@ class PeerOp:
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_forward_host(self.handle, C.byref(t), x.shape[0]))
 
+    def forward_host_async(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None) -> int:
+        """Submit one host-buffer batch and return its ticket; ``forward_host_wait(ticket)`` blocks until ``out``
+        (and the optional id/score outputs) are complete.  x must not change and out must not be read before."""
+        if x.device.type != "cpu" or out.device.type != "cpu":
+            raise RuntimeError("forward_host_async takes host tensors for x and out")
+        t = self._tensors(x, w, out, ids_out, scores_out, host_io=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        ticket = C.c_int64(-1)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_forward_host_async(self.handle, C.byref(t), x.shape[0], C.byref(ticket)))
+        return int(ticket.value)
+
+    def forward_host_wait(self, ticket: int):
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_forward_host_wait(self.handle, int(ticket)))
+
     def project_queries(self, x: torch.Tensor, w: dict) -> torch.Tensor:
         T = x.shape[0]
         q = torch.empty(T, self.cfg.num_heads, self.cfg.query_dim, dtype=torch.float32, device=self.device)
@@ -501,6 +517,22 @@ class PEER(nn.Module):
     def forward_host(self, hidden_states: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Same layer for a HOST tensor (pinned for full speed): slices are copied to the device,
         processed and copied back on overlapping streams.  Returns a host tensor.  Inference only."""
+        return self._forward_host(hidden_states, out, blocking=True)[0]
+
+    def forward_host_wait(self, ticket) -> None:
+        """Block until the batch submitted by ``forward_host_async`` has landed in its host output."""
+        op, tk = ticket
+        op.forward_host_wait(tk)
+
+    def forward_host_async(self, hidden_states: torch.Tensor, out: Optional[torch.Tensor] = None):
+        """Submit a host batch without waiting: returns ``(out, ticket)``.  The next batch may be submitted
+        before this one is waited for, so that its first copy-in overlaps this one's last copy-out; give
+        each batch in flight its own ``out``.  ``hidden_states`` must not change until the wait.  A batch
+        submitted this way runs as one slice (its copies hide behind its neighbours' kernels); the blocking
+        call slices a batch so that its own copies overlap its own kernels."""
+        return self._forward_host(hidden_states, out, blocking=False)
+
+    def _forward_host(self, hidden_states: torch.Tensor, out: Optional[torch.Tensor], blocking: bool):
         if self._needs_grad(hidden_states):
             raise RuntimeError("forward_host is an inference path; call it under torch.no_grad()")
         if self.training and self.dropout.p > 0:
@@ -519,9 +551,13 @@ class PEER(nn.Module):
         if self.track_indices:
             ids = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.int64, pin_memory=True)
             sc = torch.empty(T, self.num_heads, self.num_experts_per_tok, dtype=torch.float32, pin_memory=True)
-        op.forward_host(x, w, out.view(T, self.output_dim), ids, sc)
-        self._stash(ids, sc, B, S)
-        return out
+        ticket = None
+        if blocking:
+            op.forward_host(x, w, out.view(T, self.output_dim), ids, sc)
+        else:
+            ticket = (op, op.forward_host_async(x, w, out.view(T, self.output_dim), ids, sc))
+        self._stash(ids, sc, B, S)          # complete after the wait
+        return out, ticket
 
     def _stash(self, ids, sc, B, S):
         if ids is not None:

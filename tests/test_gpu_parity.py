@@ -259,6 +259,25 @@ def test_host_buffer_path_equals_device_path(cuda_device):
     assert torch.equal(m._last_expert_indices, ids_dev.cpu())
 
 
+def test_host_batches_in_flight_together(cuda_device):
+    """Three batches submitted back to back before any is waited for; each lands in its own buffer."""
+    cfg = syn.scaled(syn.CONFIGS["c2"], product_key_dim=(64, 64), batch=2, seq=2500)     # two slices per batch
+    sd = syn.make_weights(cfg, 12, cuda_device)
+    m = _module(cfg, sd, cuda_device, "product")
+    xs = [syn.make_input(cfg, 20 + i, "cpu").pin_memory() for i in range(3)]
+    with torch.no_grad():
+        want = [m(x.to(cuda_device)).cpu() for x in xs]
+        pending = [m.forward_host_async(x) for x in xs]
+        for out, ticket in reversed(pending):                # any order
+            m.forward_host_wait(ticket)
+        for (out, _), w in zip(pending, want):
+            assert torch.equal(out, w)
+        y = m.forward_host(xs[1])                             # the blocking call still works afterwards
+    assert torch.equal(y, want[1])
+    with pytest.raises(ValueError, match="ticket"):
+        m._op.forward_host_wait(10 ** 6)
+
+
 def test_slicing_by_max_tokens_is_transparent(cuda_device):
     cfg, sd, x, rec = load_golden("c1")
     _, _, out_a, ids_a, _ = run_layer(cfg, sd, x, cuda_device, max_tokens=256)
