@@ -167,7 +167,7 @@ def make_layer(cfg, args, device):
 def time_backward(layer, cfg, x, steps):
     """Forward+backward of the layer (all parameters and x require gradients), and the expert-stage
     gradient kernel on its own.  Algorithmic bytes of that kernel per (token, slot): the two table rows
-    read, and the two fp32 gradient rows read and written."""
+    read, and the two gradient rows (same dtype) read and written."""
     T, HK = cfg.tokens, cfg.num_heads * cfg.top_k
     layer.requires_grad_(True)
     xg = x.clone().requires_grad_(True)
@@ -190,19 +190,20 @@ def time_backward(layer, cfg, x, steps):
     op = layer._op
     ids = layer._last_expert_indices.view(T, HK).to(torch.int32)
     w = torch.softmax(layer._last_expert_scores.view(T, cfg.num_heads, cfg.top_k), -1).view(T, HK).contiguous()
-    gd = torch.zeros(layer.expert_down.weight.shape, dtype=torch.float32, device=x.device)
-    gu = torch.zeros(layer.expert_up.weight.shape, dtype=torch.float32, device=x.device)
+    gdt = cfg.table_dtype                      # the sums are formed in the tables' dtype, as in the training step
+    gd = torch.zeros(layer.expert_down.weight.shape, dtype=gdt, device=x.device)
+    gu = torch.zeros(layer.expert_up.weight.shape, dtype=gdt, device=x.device)
     x2, g2 = x.view(T, -1), grad_out.view(T, -1)
     for i in range(1 + 3):
         if i == 1:
             ev[2].record()
-        op.gather_eval_backward(x2, g2, ids, w, layer.expert_down.weight, layer.expert_up.weight, gd, gu)
+        op.gather_eval_backward(x2, g2, ids, w, layer.expert_down.weight, layer.expert_up.weight, gd, gu, grad_dtype=gdt)
     ev[3].record()
     torch.cuda.synchronize()
     op.query_status()
     k_ms = ev[2].elapsed_time(ev[3]) / 3
     eb = torch.empty(0, dtype=cfg.table_dtype).element_size()
-    bytes_alg = T * HK * (cfg.input_dim + cfg.output_dim) * (eb + 8)
+    bytes_alg = T * HK * (cfg.input_dim + cfg.output_dim) * (eb + 2 * eb)     # rows read; gradient rows read and written
     peak, kind = hbm_peak()
     return {"fwd_bwd_ms_per_step": step_ms, "fwd_bwd_tokens_per_s": T / (step_ms / 1e3), "steps": steps,
             "gather_grad_kernel_ms": k_ms, "algorithmic_bytes_per_launch": bytes_alg,

@@ -185,13 +185,16 @@ int peer_gather_eval_partial(peer_handle_t h, const void* x, const int32_t* ids,
  * (act_dtype) and the forward's x, ids and weights:
  *   grad_x       [T, input_dim]      fp32, written:  sum_j dz_j * down[ids_j]
  *   grad_weights [T, num_heads*top_k] fp32, written: act(down[ids_j] . x) * (up[ids_j] . grad_out)
- *   grad_down    [num_experts, input_dim]  fp32, ACCUMULATED: += dz_j * x          (zero it first)
- *   grad_up      [num_experts, output_dim] fp32, ACCUMULATED: += w_j * act(.) * grad_out
- * with dz_j = w_j * (up[ids_j] . grad_out) * act'(down[ids_j] . x).  Tables must be in act_dtype. */
+ *   grad_down    [num_experts, input_dim]  ACCUMULATED: += dz_j * x          (zero it first)
+ *   grad_up      [num_experts, output_dim] ACCUMULATED: += w_j * act(.) * grad_out
+ * with dz_j = w_j * (up[ids_j] . grad_out) * act'(down[ids_j] . x).  Tables must be in act_dtype.
+ * grad_table_dtype: PEER_DTYPE_F32, or PEER_DTYPE_BF16 for a bf16 layer: the sums are then formed in
+ * bf16, as the reference's bf16 training forms them (its embedding gradients are bf16 tensors), with
+ * half the memory traffic and no cast afterwards. */
 int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
                               const float* weights, const void* expert_down, const void* expert_up,
-                              float* grad_x, float* grad_weights, float* grad_down, float* grad_up,
-                              int64_t n_tokens, void* stream);
+                              float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
+                              int32_t grad_table_dtype, int64_t n_tokens, void* stream);
 
 /* Product-key retrieval (same result as peer_select) for callers that cannot allocate device
  * memory: no handle, no cudaMalloc anywhere on this path.  This entry point has no counterpart in

@@ -16,8 +16,8 @@ Here the stages are
   softmax, optional dropout of the expert activations (experts.py:366; a
   per-slot factor, folded into the weights because each expert has one neuron);
 * expert evaluation: ``peer_gather_eval`` forward, ``peer_gather_eval_backward``
-  backward (``_ExpertEval``): dense fp32 table gradients accumulated with vector
-  reductions, cast to the parameters' dtype at the end.
+  backward (``_ExpertEval``): dense table gradients accumulated with vector
+  reductions, in the parameters' own dtype for single-neuron experts.
 """
 from __future__ import annotations
 
@@ -59,7 +59,11 @@ class _ExpertEval(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         x, weights, ids32, down, up = ctx.saved_tensors
-        gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up)
+        # single-neuron experts of a bf16 layer: the table gradients are summed in bf16, in the buffers that become
+        # the parameters' .grad (the reference's bf16 training sums them in bf16 too); otherwise fp32, then cast
+        direct = ctx.op.cfg.expert_hidden_size == 1
+        gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up,
+                                                     grad_dtype=down.dtype if direct else torch.float32)
         need = ctx.needs_input_grad
         return (gx.to(x.dtype) if need[0] else None, gw if need[1] else None, None,
                 gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None)

@@ -18,6 +18,8 @@
 // accumulated with vector reductions (red.global.add.v4.f32) into fp32 tables,
 // so tokens that share an expert need no sorting or locking.  Rows are read
 // twice (dot products, then the updates); the second read hits L1/L2.
+#include <type_traits>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -30,6 +32,14 @@ constexpr int THREADS = WARPS * 32;
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
     asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ void red_add_v4_bf16x2(void* addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // one 16-byte chunk of a row (table or activation storage) as fp32 values
@@ -62,14 +72,16 @@ __device__ __forceinline__ float act_slope(float z, int activation) {
 struct GradParams {
     const void* x; const void* dy; const int32_t* ids; const float* weights;
     const char* down; const char* up;
-    float* d_down; float* d_up; float* dx; float* dweights;
+    void* d_down; void* d_up; float* dx; float* dweights;
     int64_t T; int HK; int64_t N; int D, Dout; int activation; int* status;
     int nch_u, nch_v;          // 16-byte chunks per down / up row (table storage)
 };
 
 // XT = TT here (fp32 layer with fp32 tables, bf16 layer with bf16 tables), so a 16-byte chunk of x or
 // dy covers the same elements as a 16-byte chunk of a table row.
-template <typename XT, int CH>
+// LP: the table gradients are accumulated in the tables' own 16-bit type (what the reference's bf16 training
+// does: its embedding gradients are bf16) instead of fp32: half the read-modify-write bytes, no cast afterwards.
+template <typename XT, int CH, bool LP>
 __global__ void __launch_bounds__(THREADS) gather_grad_kernel(const GradParams p) {
     constexpr int EPC = Chunk16<XT>::N;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -121,26 +133,37 @@ __global__ void __launch_bounds__(THREADS) gather_grad_kernel(const GradParams p
             if (lane == 0) p.dweights[t * p.HK + e] = av * g;
             const float cv = w * av;
             const float dz = w * g * act_slope(z, p.activation);
-            float* __restrict__ du = p.d_down + static_cast<int64_t>(id) * p.D;
-            float* __restrict__ dv = p.d_up + static_cast<int64_t>(id) * p.Dout;
+            using GT = typename std::conditional<LP, XT, float>::type;
+            GT* __restrict__ du = static_cast<GT*>(p.d_down) + static_cast<int64_t>(id) * p.D;
+            GT* __restrict__ dv = static_cast<GT*>(p.d_up) + static_cast<int64_t>(id) * p.Dout;
 #pragma unroll
             for (int i = 0; i < CH; ++i) {
                 const int c = lane + 32 * i;
                 float a[EPC], b[EPC];
                 if (c < p.nch_v) {
                     Chunk16<XT>::decode(dyc[i], b);
+                    if constexpr (LP && sizeof(XT) == 2) {
+                        red_add_v4_bf16x2(dv + c * EPC, pack2(cv * b[0], cv * b[1]), pack2(cv * b[2], cv * b[3]),
+                                          pack2(cv * b[4], cv * b[5]), pack2(cv * b[6], cv * b[7]));
+                    } else {
 #pragma unroll
-                    for (int q = 0; q < EPC; q += 4)
-                        red_add_v4(dv + c * EPC + q, cv * b[q], cv * b[q + 1], cv * b[q + 2], cv * b[q + 3]);
+                        for (int q = 0; q < EPC; q += 4)
+                            red_add_v4(reinterpret_cast<float*>(dv) + c * EPC + q, cv * b[q], cv * b[q + 1], cv * b[q + 2], cv * b[q + 3]);
+                    }
                 }
                 if (c < p.nch_u) {
                     Chunk16<XT>::decode(__ldg(ur + c), a);
                     Chunk16<XT>::decode(xc[i], b);
 #pragma unroll
                     for (int q = 0; q < EPC; ++q) dxa[i * EPC + q] = fmaf(dz, a[q], dxa[i * EPC + q]);
+                    if constexpr (LP && sizeof(XT) == 2) {
+                        red_add_v4_bf16x2(du + c * EPC, pack2(dz * b[0], dz * b[1]), pack2(dz * b[2], dz * b[3]),
+                                          pack2(dz * b[4], dz * b[5]), pack2(dz * b[6], dz * b[7]));
+                    } else {
 #pragma unroll
-                    for (int q = 0; q < EPC; q += 4)
-                        red_add_v4(du + c * EPC + q, dz * b[q], dz * b[q + 1], dz * b[q + 2], dz * b[q + 3]);
+                        for (int q = 0; q < EPC; q += 4)
+                            red_add_v4(reinterpret_cast<float*>(du) + c * EPC + q, dz * b[q], dz * b[q + 1], dz * b[q + 2], dz * b[q + 3]);
+                    }
                 }
             }
         }
@@ -157,23 +180,23 @@ __global__ void __launch_bounds__(THREADS) gather_grad_kernel(const GradParams p
     }
 }
 
-template <typename XT, int CH>
+template <typename XT, int CH, bool LP>
 cudaError_t launch_t(const GradParams& p, int sm_count, cudaStream_t s) {
     int64_t ctas = (p.T + WARPS - 1) / WARPS;
     const int64_t cap = static_cast<int64_t>(sm_count) * 4;      // a few CTAs per SM, grid-stride over tokens
     if (ctas > cap) ctas = cap;
-    gather_grad_kernel<XT, CH><<<static_cast<unsigned>(ctas), THREADS, 0, s>>>(p);
+    gather_grad_kernel<XT, CH, LP><<<static_cast<unsigned>(ctas), THREADS, 0, s>>>(p);
     return cudaGetLastError();
 }
 
-template <typename XT>
+template <typename XT, bool LP>
 cudaError_t launch_ch(const GradParams& p, int sm_count, cudaStream_t s) {
     const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
     const int need = (max_ch + 31) / 32;
-    if (need <= 1) return launch_t<XT, 1>(p, sm_count, s);
-    if (need <= 2) return launch_t<XT, 2>(p, sm_count, s);
-    if (need <= 4) return launch_t<XT, 4>(p, sm_count, s);
-    if (need <= 8) return launch_t<XT, 8>(p, sm_count, s);
+    if (need <= 1) return launch_t<XT, 1, LP>(p, sm_count, s);
+    if (need <= 2) return launch_t<XT, 2, LP>(p, sm_count, s);
+    if (need <= 4) return launch_t<XT, 4, LP>(p, sm_count, s);
+    if (need <= 8) return launch_t<XT, 8, LP>(p, sm_count, s);
     return cudaErrorInvalidValue;
 }
 
@@ -190,8 +213,10 @@ cudaError_t launch_gather_grad(const GatherGradArgs& a, cudaStream_t s) {
     p.d_down = a.d_down; p.d_up = a.d_up; p.dx = a.dx; p.dweights = a.dweights;
     p.T = a.T; p.HK = a.HK; p.N = a.N; p.D = a.D; p.Dout = a.Dout; p.activation = a.activation; p.status = a.status;
     p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
-    if (a.act_dtype == PEER_DTYPE_F32) return launch_ch<float>(p, a.sm_count, s);
-    if (a.act_dtype == PEER_DTYPE_BF16) return launch_ch<__nv_bfloat16>(p, a.sm_count, s);
+    if (a.act_dtype == PEER_DTYPE_F32) return launch_ch<float, false>(p, a.sm_count, s);       // fp32 either way
+    if (a.act_dtype == PEER_DTYPE_BF16)
+        return a.grad_dtype == PEER_DTYPE_BF16 ? launch_ch<__nv_bfloat16, true>(p, a.sm_count, s)
+                                               : launch_ch<__nv_bfloat16, false>(p, a.sm_count, s);
     return cudaErrorInvalidValue;
 }
 

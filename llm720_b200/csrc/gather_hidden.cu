@@ -105,8 +105,8 @@ __global__ void __launch_bounds__(THREADS) gather_hidden_grad_kernel(const Gathe
             }
             const T* ub = down + static_cast<int64_t>(id) * h * a.D;
             const T* vb = up + static_cast<int64_t>(id) * h * a.Dout;
-            float* du = a.d_down + static_cast<int64_t>(id) * h * a.D;
-            float* dv = a.d_up + static_cast<int64_t>(id) * h * a.Dout;
+            float* du = static_cast<float*>(a.d_down) + static_cast<int64_t>(id) * h * a.D;
+            float* dv = static_cast<float*>(a.d_up) + static_cast<int64_t>(id) * h * a.Dout;
             float z[MAX_H], g[MAX_H];
 #pragma unroll
             for (int m = 0; m < MAX_H; ++m) {
@@ -193,7 +193,8 @@ cudaError_t launch_gather_hidden(const GatherArgs& a, cudaStream_t s) {
 
 cudaError_t launch_gather_hidden_grad(const GatherGradArgs& a, cudaStream_t s) {
     if (a.T == 0) return cudaSuccess;
-    if (a.hidden < 1 || a.hidden > MAX_H || a.act_dtype != a.table_dtype) return cudaErrorInvalidValue;
+    if (a.hidden < 1 || a.hidden > MAX_H || a.act_dtype != a.table_dtype || a.grad_dtype != PEER_DTYPE_F32)
+        return cudaErrorInvalidValue;
     const size_t smem = sizeof(float) * WARPS * a.D;
     cudaError_t e;
     if (a.act_dtype == PEER_DTYPE_F32) {

@@ -119,8 +119,8 @@ struct GatherGradArgs {
     const float* weights;     // [T, HK]
     const void* down;         // [N, D]
     const void* up;           // [N, Dout]
-    float* d_down;            // [N, D] fp32, accumulated into
-    float* d_up;              // [N, Dout] fp32, accumulated into
+    void* d_down;             // [N, D] fp32 (or grad_dtype), accumulated into
+    void* d_up;               // [N, Dout] fp32 (or grad_dtype), accumulated into
     float* dx;                // [T, D] fp32, written
     float* dweights;          // [T, HK] fp32, written
     int64_t T;
@@ -131,6 +131,7 @@ struct GatherGradArgs {
     int* status;
     int sm_count;
     int hidden;               // neurons per expert; 0 or 1 = single
+    int grad_dtype;           // dtype of d_down / d_up: PEER_DTYPE_F32, or the tables' own 16-bit type
 };
 cudaError_t launch_gather_grad(const GatherGradArgs& a, cudaStream_t s);
 

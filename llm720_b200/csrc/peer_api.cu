@@ -742,8 +742,8 @@ extern "C" int peer_gather_eval_partial(peer_handle_t h, const void* x, const in
 
 extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
                                          const float* weights, const void* expert_down, const void* expert_up,
-                                         float* grad_x, float* grad_weights, float* grad_down, float* grad_up,
-                                         int64_t n_tokens, void* stream) {
+                                         float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
+                                         int32_t grad_table_dtype, int64_t n_tokens, void* stream) {
     if (!h) return PEER_ERR_INVALID_ARG;
     if (n_tokens == 0) return PEER_OK;
     const peer_config_t& c = h->cfg;
@@ -751,6 +751,8 @@ extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const v
         return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_backward: null pointer");
     if (c.table_dtype != c.act_dtype)
         return fail(h, PEER_ERR_UNSUPPORTED, "backward needs tables in the layer's dtype (fp32 or bf16); quantised tables are inference-only");
+    if (grad_table_dtype != PEER_DTYPE_F32 && (grad_table_dtype != c.table_dtype || h->hidden > 1))
+        return fail(h, PEER_ERR_UNSUPPORTED, "table gradients are accumulated in fp32, or (single-neuron experts) in the tables' own dtype");
     if (!aligned16(x) || !aligned16(grad_out) || !aligned16(expert_down) || !aligned16(expert_up) || !aligned16(grad_x) ||
         !aligned16(grad_down) || !aligned16(grad_up))
         return fail(h, PEER_ERR_INVALID_ARG, "x, grad_out, tables and gradient buffers must be 16-byte aligned");
@@ -759,7 +761,7 @@ extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const v
     g.d_down = grad_down; g.d_up = grad_up; g.dx = grad_x; g.dweights = grad_weights;
     g.T = n_tokens; g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
-    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden;
+    g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.grad_dtype = grad_table_dtype;
     cudaError_t e = h->hidden > 1 ? launch_gather_hidden_grad(g, static_cast<cudaStream_t>(stream))
                                   : launch_gather_grad(g, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue)

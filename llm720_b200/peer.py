@@ -251,10 +251,13 @@ class PeerOp:
                 _ptr(down_scale), _ptr(up_scale), down.shape[0], _ptr(out), T, _stream(self.device)))
         return out
 
-    def gather_eval_backward(self, x, grad_out, ids32, weights, down, up, grad_down=None, grad_up=None):
+    def gather_eval_backward(self, x, grad_out, ids32, weights, down, up, grad_down=None, grad_up=None,
+                             grad_dtype: torch.dtype = torch.float32):
         """Gradients of ``gather_eval``.  Returns (grad_x [T,D] fp32, grad_weights [T,H*k] fp32, grad_down
-        [N,D] fp32, grad_up [N,D_out] fp32); the two table gradients are accumulated into the buffers
-        passed in (zero-initialised ones are made when none are given)."""
+        [N,D], grad_up [N,D_out]); the two table gradients are accumulated into the buffers passed in
+        (zero-initialised ones are made when none are given), in ``grad_dtype``: fp32, or the tables' bf16."""
+        if grad_dtype not in (torch.float32, self.table_dtype) or grad_dtype not in _DT:
+            raise ValueError(f"table gradients are accumulated in fp32 or in the tables' dtype, not {grad_dtype}")
         self._dev(x, "x", self.act_dtype)
         self._dev(grad_out, "grad_out", self.act_dtype)
         self._dev(ids32, "ids", torch.int32)
@@ -263,17 +266,17 @@ class PeerOp:
         self._dev(up, "expert_up", self.table_dtype)
         T = x.shape[0]
         if grad_down is None:
-            grad_down = torch.zeros(down.shape, dtype=torch.float32, device=self.device)
+            grad_down = torch.zeros(down.shape, dtype=grad_dtype, device=self.device)
         if grad_up is None:
-            grad_up = torch.zeros(up.shape, dtype=torch.float32, device=self.device)
-        self._dev(grad_down, "grad_down", torch.float32)
-        self._dev(grad_up, "grad_up", torch.float32)
+            grad_up = torch.zeros(up.shape, dtype=grad_dtype, device=self.device)
+        self._dev(grad_down, "grad_down", grad_dtype)
+        self._dev(grad_up, "grad_up", grad_dtype)
         gx = torch.empty(T, self.cfg.input_dim, dtype=torch.float32, device=self.device)
         gw = torch.empty(T, self.cfg.num_heads * self.cfg.top_k, dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_gather_eval_backward(
                 self.handle, _ptr(x), _ptr(grad_out), _ptr(ids32), _ptr(weights), _ptr(down), _ptr(up),
-                _ptr(gx), _ptr(gw), _ptr(grad_down), _ptr(grad_up), T, _stream(self.device)))
+                _ptr(gx), _ptr(gw), _ptr(grad_down), _ptr(grad_up), _DT[grad_dtype], T, _stream(self.device)))
         return gx, gw, grad_down, grad_up
 
     def query_status(self):

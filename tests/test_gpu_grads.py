@@ -73,6 +73,31 @@ def test_expert_stage_backward_from_given_selections(cuda_device, dtype, D, Dout
     assert rel_err(gd.cpu(), 2 * leaves[2].grad) < tol and rel_err(gu.cpu(), 2 * leaves[3].grad) < tol
 
 
+def test_expert_stage_backward_with_sums_in_bf16(cuda_device):
+    """Table gradients accumulated in bf16 (what a bf16 training run keeps): few contributions per row, so the
+    result is the fp32 sum to within a few bf16 roundings."""
+    D, Dout, H, k, N, T = 2048, 2048, 8, 16, 8192, 64
+    g = torch.Generator().manual_seed(7)
+    cfg = syn.PeerConfig("t", D, Dout, H, 32, (N, 1), k, torch.bfloat16, torch.bfloat16, 1, T)
+    op = make_op(cfg, cuda_device)
+    dev = lambda t: t.to(cuda_device)
+    x, dy = dev(torch.randn(T, D, generator=g).bfloat16()), dev(torch.randn(T, Dout, generator=g).bfloat16())
+    down = dev((torch.randn(N, D, generator=g) * D ** -0.5).bfloat16())
+    up = dev((torch.randn(N, Dout, generator=g) * D ** -0.5).bfloat16())
+    ids = dev(torch.randint(0, N, (T, H * k), generator=g, dtype=torch.int32))
+    w = dev(torch.rand(T, H * k, generator=g))
+    gx, gw, gd, gu = op.gather_eval_backward(x, dy, ids, w, down, up)                       # fp32 sums
+    gx2, gw2, gd2, gu2 = op.gather_eval_backward(x, dy, ids, w, down, up, grad_dtype=torch.bfloat16)
+    op.query_status()
+    assert gd2.dtype == torch.bfloat16 and gu2.dtype == torch.bfloat16
+    assert torch.equal(gx, gx2) and torch.equal(gw, gw2)
+    for a, b in ((gd2, gd), (gu2, gu)):
+        l1 = float((a.float() - b).abs().sum() / b.abs().sum())
+        assert l1 < 4e-3 and rel_err(a.float().cpu(), b.cpu()) < 1e-2, l1
+    with pytest.raises(ValueError):
+        op.gather_eval_backward(x, dy, ids, w, down, up, grad_dtype=torch.float16)
+
+
 def test_backward_skips_out_of_range_ids(cuda_device):
     cfg = syn.PeerConfig("t", 32, 32, 1, 32, (16, 1), 2, torch.float32, torch.float32, 1, 3)
     op = make_op(cfg, cuda_device)
