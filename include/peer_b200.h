@@ -86,6 +86,9 @@ typedef struct peer_tensors {
     float*       scores_out;   /* optional [T, num_heads, top_k]: raw (pre-softmax) scores */
     const void*  keys2;        /* [n_keys2, query_dim/num_key_dims] (3-D, 4-D key grids) */
     const void*  keys3;        /* [n_keys3, query_dim/num_key_dims] (4-D key grids)      */
+    int32_t*     product_ids_out; /* optional [T, num_heads, top_k] (peer_forward only): the selected experts'
+                                  true positions in the key grid, sum_d index_d * stride_d, whatever
+                                  index_mode says; the backward pass needs the per-dimension indices */
 } peer_tensors_t;
 
 typedef struct peer_op* peer_handle_t;

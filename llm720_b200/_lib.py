@@ -31,7 +31,7 @@ class PeerConfig(C.Structure):
 class PeerTensors(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "x", "query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1", "expert_down", "expert_up",
-        "down_scale", "up_scale", "out", "ids_out", "scores_out", "keys2", "keys3")]
+        "down_scale", "up_scale", "out", "ids_out", "scores_out", "keys2", "keys3", "product_ids_out")]
 
 
 EXPORTS = {

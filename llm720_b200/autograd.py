@@ -3,7 +3,9 @@ the gradients of the expert stage; torch operations for the small rest.
 
 The reference trains through its PyTorch forward (llm/models/experts.py:
 288-384; llm/training/train.py:743-768), with autograd deriving every gradient.
-Here the stages are
+Without dropout the whole layer is ONE autograd node (``_FusedLayer``): its forward is the inference path
+unchanged, its backward the expert-stage gradient kernel plus a torch re-derivation of the score path.  With
+dropout (training mode) the stages are separate nodes:
 
 * query projection + LayerNorm: value from the library's query kernel (fp32);
   gradient by re-running ``F.linear`` / ``F.layer_norm`` in backward
@@ -69,21 +71,114 @@ class _ExpertEval(torch.autograd.Function):
                 gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None)
 
 
+def _key_grid(module):
+    dims = list(module.product_key_dim)
+    strides = [1] * len(dims)                               # true row-major strides of the key grid
+    for d in range(len(dims) - 2, -1, -1):
+        strides[d] = strides[d + 1] * dims[d + 1]
+    return dims, strides
+
+
+def _selected_scores(module, q, idx):
+    """Scores of the selected experts from queries q [T,H,Q] (after LayerNorm) and the per-dimension indices
+    idx[d] [T,H,k]: sum_d q_d . k_d[idx_d], with the normalisations of experts.py:153-163.  Differentiable in
+    q; the sub-keys are read detached, as the reference reads them through ``.data``."""
+    nd = len(idx)
+    width = module.query_dim // nd
+    scores = 0
+    for d in range(nd):
+        qd = q[..., d * width:(d + 1) * width]
+        kd = module.sub_keys[d].detach().float()
+        if module.norm_keys:
+            kd = F.normalize(kd, dim=-1)
+        if module.norm_query:
+            qd = F.normalize(qd, dim=-1)
+        scores = scores + (qd.unsqueeze(2) * kd[idx[d]]).sum(-1)
+    return scores
+
+
+class _FusedLayer(torch.autograd.Function):
+    """The whole layer as one node: forward is the inference path (query, select and expert kernels, with the
+    selected experts' grid positions as an extra output); backward runs the expert-stage gradient kernel and
+    re-derives the score path (projection, LayerNorm, normalisation, the k selected scores, softmax) with torch
+    operations to push the weight gradients back to x and the query parameters."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, ln_w, ln_b, down, up, module):
+        T = x.shape[0]
+        H, k = module.num_heads, module.num_experts_per_tok
+        op = module._operator(x.device, x.dtype, T)
+        out = torch.empty(T, module.output_dim, dtype=x.dtype, device=x.device)
+        ids = torch.empty(T, H, k, dtype=torch.int64, device=x.device)
+        sc = torch.empty(T, H, k, dtype=torch.float32, device=x.device)
+        pid = torch.empty(T, H, k, dtype=torch.int32, device=x.device)
+        op.forward(x, module._weights(), out, ids, sc, pid)
+        ctx.save_for_backward(x, weight, bias, ln_w, ln_b, down, up, ids, sc, pid)
+        ctx.module, ctx.op = module, op
+        ctx.mark_non_differentiable(ids, sc)
+        return out, ids, sc
+
+    @staticmethod
+    def backward(ctx, grad_out, _gi, _gs):
+        x, weight, bias, ln_w, ln_b, down, up, ids, sc, pid = ctx.saved_tensors
+        module, op = ctx.module, ctx.op
+        T = x.shape[0]
+        H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
+        need = ctx.needs_input_grad
+        weights = torch.softmax(sc, dim=-1).view(T, H * k)
+        direct = module.expert_hidden_size == 1
+        gx, gw, gd, gu = op.gather_eval_backward(x, grad_out.contiguous(), ids.view(T, H * k).to(torch.int32), weights,
+                                                 down, up, grad_dtype=down.dtype if direct else torch.float32)
+        # score path: d(loss)/d(weights) = gw, pushed through softmax, the selected scores and the query path
+        leaves = [None if t is None else t.detach().requires_grad_(n)
+                  for t, n in zip((x, weight, bias, ln_w, ln_b), need[:5])]
+        wanted = [t for t in leaves if t is not None and t.requires_grad]
+        got = iter(())
+        if wanted:
+            dims, strides = _key_grid(module)
+            pid64 = pid.long()
+            idx = [torch.div(pid64, strides[d], rounding_mode="floor") % dims[d] for d in range(len(dims))]
+            with torch.enable_grad():
+                q = F.linear(leaves[0], leaves[1], leaves[2]).float().view(T, H, Q)
+                if leaves[3] is not None:
+                    q = F.layer_norm(q, (Q,), leaves[3].float(), None if leaves[4] is None else leaves[4].float(), 1e-5)
+                w2 = torch.softmax(_selected_scores(module, q, idx), dim=-1)
+            got = iter(torch.autograd.grad(w2, wanted, gw.view(T, H, k)))
+        grads = [next(got) if (t is not None and t.requires_grad) else None for t in leaves]
+        if need[0]:
+            grads[0] = (gx + grads[0].float()).to(x.dtype)
+        return (*grads, gd.to(down.dtype) if need[5] else None, gu.to(up.dtype) if need[6] else None, None)
+
+
 def peer_forward_autograd(module, hidden_states: torch.Tensor) -> torch.Tensor:
     """Forward of ``module`` (a ``llm720_b200.PEER``) that records an autograd graph."""
     w = module._weights()
     if w["down_scale"] is not None:
         raise RuntimeError("quantised (FP8) expert tables are inference-only: no backward pass")
-    dt = module.query_proj.weight.dtype
     B, S, _ = hidden_states.shape
     T = B * S
-    H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
-    dims = list(module.product_key_dim)
-    nd = len(dims)
-    strides = [1] * nd                                      # true row-major strides of the key grid
-    for d in range(nd - 2, -1, -1):
-        strides[d] = strides[d + 1] * dims[d + 1]
     x = hidden_states.contiguous().view(T, module.input_dim)
+    ln = module.query_layer_norm
+    if not (module.training and module.dropout.p > 0):
+        out, ids, sc = _FusedLayer.apply(x, module.query_proj.weight, module.query_proj.bias,
+                                         None if ln is None else ln.weight, None if ln is None else ln.bias,
+                                         module.expert_down.weight, module.expert_up.weight, module)
+        if module.track_indices:
+            module._stash(ids, sc, B, S)
+        return out.view(B, S, module.output_dim)
+    return _forward_with_dropout(module, x, w, B, S)
+
+
+def _forward_with_dropout(module, x, w, B, S):
+    """Training mode with dropout of the expert activations (experts.py:366): the stages as separate autograd
+    nodes, so that the per-slot dropout factor can sit between the softmax and the expert stage."""
+    if module.expert_hidden_size != 1:
+        raise RuntimeError("dropout with expert_hidden_size > 1 is not implemented (it acts on every neuron)")
+    T = B * S
+    dt = x.dtype
+    H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
+    dims, strides = _key_grid(module)
+    nd = len(dims)
     op = module._operator(x.device, dt, T)
     ln = module.query_layer_norm
     q = _ProjectQueries.apply(x, module.query_proj.weight, module.query_proj.bias,
@@ -102,21 +197,9 @@ def peer_forward_autograd(module, hidden_states: torch.Tensor) -> torch.Tensor:
             flat = torch.arange(k, device=pid.device).expand_as(pid).contiguous()
         else:
             flat = pid
-    width = Q // nd
-    scores = 0
-    for d in range(nd):
-        qd = q[..., d * width:(d + 1) * width]
-        kd = keys[d].float()
-        if module.norm_keys:
-            kd = F.normalize(kd, dim=-1)
-        if module.norm_query:
-            qd = F.normalize(qd, dim=-1)
-        scores = scores + (qd.unsqueeze(2) * kd[idx[d]]).sum(-1)                # [T, H, k]
+    scores = _selected_scores(module, q, idx)
     weights = torch.softmax(scores, dim=-1)
-    if module.training and module.dropout.p > 0:
-        if module.expert_hidden_size != 1:
-            raise RuntimeError("dropout with expert_hidden_size > 1 is not implemented (it acts on every neuron)")
-        weights = weights * F.dropout(torch.ones_like(weights), module.dropout.p, True)
+    weights = weights * F.dropout(torch.ones_like(weights), module.dropout.p, True)
     out = _ExpertEval.apply(x, weights.view(T, H * k), flat.to(torch.int32).view(T, H * k),
                             module.expert_down.weight, module.expert_up.weight, op)
     if module.track_indices:

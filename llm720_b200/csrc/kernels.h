@@ -45,6 +45,7 @@ struct SelectTcArgs {
     int64_t rows;                  // T * H
     int Q, n0, n1, kp0, kp1, k, mult0, mult1;
     int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores;   // as in SelectArgs
+    int32_t* prod_ids;        // optional [rows, k]: i0 * n1 + i1 whatever mult0/mult1 say
     int* status;
     int sm_count;
     int32_t* overflow_rows;        // [rows]: rows the kernel leaves to the exact kernel (clustered scores)
@@ -79,6 +80,7 @@ struct SelectArgs {
     float* weights;       // optional [rows, k] softmax over k
     int64_t* ids64;       // optional [rows, k]
     float* raw_scores;    // optional [rows, k]
+    int32_t* prod_ids;    // optional [rows, k]: i0 * n1 + i1 whatever mult0/mult1 say
     // optional: process only the rows row_list[0 .. *row_count) (device memory), and/or take the
     // normalised queries as the sum of three bf16 terms split_stride elements apart
     const int32_t* row_list;
@@ -154,6 +156,8 @@ struct SelectNdArgs {
     float* weights;           // optional [rows, k] softmax
     int64_t* ids64;           // optional [rows, k]
     float* raw_scores;        // optional [rows, k]
+    int32_t* prod_ids;        // optional [rows, k]: sum_d index_d * stride[d] (true row-major position in the key grid)
+    long long stride[4];
 };
 cudaError_t launch_select_nd(const SelectNdArgs& a, cudaStream_t s);
 

@@ -346,7 +346,8 @@ static SelectArgs select_args(peer_op* h, int64_t n_tokens) {
 
 // One slice (n <= max_tokens) of the layer, all pointers on the device.
 static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, void* out, int64_t* ids_out,
-                         float* scores_out, int64_t n, cudaStream_t s, const void* residual = nullptr) {
+                         float* scores_out, int64_t n, cudaStream_t s, const void* residual = nullptr,
+                         int32_t* prod_out = nullptr) {
     const peer_config_t& c = h->cfg;
     QueryArgs q{};
     q.x = x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
@@ -380,6 +381,9 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         na.nd = h->nd; na.Q = c.query_dim; na.k = c.top_k; na.norm_keys = c.norm_keys; na.norm_query = c.norm_query;
         na.act_dtype = c.act_dtype; na.rows = n * c.num_heads;
         na.ids32 = h->sel_ids; na.weights = h->sel_w; na.ids64 = ids_out; na.raw_scores = scores_out;
+        na.prod_ids = prod_out;
+        na.stride[h->nd - 1] = 1;
+        for (int d = h->nd - 2; d >= 0; --d) na.stride[d] = na.stride[d + 1] * h->n[d + 1];
         cudaError_t se = launch_select_nd(na, s);
         if (se == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "selection over this key grid is not implemented");
         CU_TRY(h, se);
@@ -390,6 +394,7 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         ta.n0 = c.n_keys0; ta.n1 = c.n_keys1; ta.kp0 = h->kp0; ta.kp1 = h->kp1; ta.k = h->k_final;
         ta.mult0 = h->mult0; ta.mult1 = h->mult1; ta.ids32 = h->sel_ids; ta.weights = h->sel_w;
         ta.ids64 = ids_out; ta.raw_scores = scores_out; ta.status = h->status; ta.sm_count = h->sm_count;
+        ta.prod_ids = prod_out;
         ta.overflow_rows = h->ovf_rows; ta.overflow_count = h->ovf_count;
         CU_TRY(h, cudaMemsetAsync(h->ovf_count, 0, sizeof(int), s));
         CU_TRY(h, launch_select_tc(ta, s));
@@ -398,11 +403,13 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         fx.q_hat = nullptr; fx.q_split = h->q_split; fx.split_stride = c.max_tokens * c.num_heads * c.query_dim;
         fx.row_list = h->ovf_rows; fx.row_count = h->ovf_count;
         fx.ids32 = h->sel_ids; fx.weights = h->sel_w; fx.ids64 = ids_out; fx.raw_scores = scores_out;
+        fx.prod_ids = prod_out;
         CU_TRY(h, launch_select_simt(fx, s));
         h->launches += 1;
     } else {
         SelectArgs sa = select_args(h, n);
         sa.ids32 = h->sel_ids; sa.weights = h->sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
+        sa.prod_ids = prod_out;
         CU_TRY(h, launch_select_simt(sa, s));
     }
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], s));
@@ -464,7 +471,8 @@ extern "C" int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_
         rc = forward_slice(h, t, static_cast<const char*>(t->x) + t0 * c.input_dim * ab,
                            static_cast<char*>(t->out) + t0 * c.output_dim * ab,
                            t->ids_out ? t->ids_out + t0 * HK : nullptr,
-                           t->scores_out ? t->scores_out + t0 * HK : nullptr, n, s);
+                           t->scores_out ? t->scores_out + t0 * HK : nullptr, n, s, nullptr,
+                           t->product_ids_out ? t->product_ids_out + t0 * HK : nullptr);
         if (rc) return rc;
     }
     return PEER_OK;

@@ -47,6 +47,7 @@ struct WarpScratch {
     int top_i[4][32];
     float run_s[2][MAX_KEEP];
     long long run_i[2][MAX_KEEP];
+    int run_p[2][MAX_KEEP];         // the same candidates' true positions in the key grid
 };
 
 template <typename T>
@@ -101,12 +102,14 @@ __global__ void __launch_bounds__(THREADS) select_nd_kernel(const SelectNdArgs a
             for (int c = lane; c < len; c += 32) {
                 w.run_s[0][c] = w.top_s[0][c];
                 w.run_i[0][c] = a.mult[0] == 0 ? c : static_cast<long long>(w.top_i[0][c]) * a.mult[0];
+                w.run_p[0][c] = w.top_i[0][c];
             }
         } else {
             len = a.kp[0];
             for (int c = lane; c < len; c += 32) {
                 w.run_s[0][c] = w.top_s[0][c];
                 w.run_i[0][c] = static_cast<long long>(w.top_i[0][c]) * a.mult[0];
+                w.run_p[0][c] = static_cast<int>(w.top_i[0][c] * a.stride[0]);
             }
             for (int d = 1; d < a.nd; ++d) {
                 __syncwarp();
@@ -119,6 +122,7 @@ __global__ void __launch_bounds__(THREADS) select_nd_kernel(const SelectNdArgs a
                     for (int c = lane; c < count; c += 32) {
                         w.run_s[nxt][c] = w.run_s[cur][c / kp] + w.top_s[d][c % kp];
                         w.run_i[nxt][c] = w.run_i[cur][c / kp] + static_cast<long long>(w.top_i[d][c % kp]) * a.mult[d];
+                        w.run_p[nxt][c] = w.run_p[cur][c / kp] + static_cast<int>(w.top_i[d][c % kp] * a.stride[d]);
                     }
                 } else {
                     int last_key = INT_MAX, last_pos = -1;   // nothing taken yet
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(THREADS) select_nd_kernel(const SelectNdArgs a
                         if (lane == 0) {
                             w.run_s[nxt][it] = key2f(m);
                             w.run_i[nxt][it] = w.run_i[cur][pos / kp] + static_cast<long long>(w.top_i[d][pos % kp]) * a.mult[d];
+                            w.run_p[nxt][it] = w.run_p[cur][pos / kp] + static_cast<int>(w.top_i[d][pos % kp] * a.stride[d]);
                         }
                         last_key = m; last_pos = pos; first = false;
                     }
@@ -160,6 +165,7 @@ __global__ void __launch_bounds__(THREADS) select_nd_kernel(const SelectNdArgs a
             if (a.weights) a.weights[o] = expf(sc - mx) / es;
             if (a.ids64) a.ids64[o] = id;
             if (a.raw_scores) a.raw_scores[o] = sc;
+            if (a.prod_ids) a.prod_ids[o] = w.run_p[cur][c];
         }
     }
 }

@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(THREADS, 2) select_simt_kernel(SelectArgs a) {
             if (a.weights) a.weights[o] = w;
             if (a.ids64) a.ids64[o] = id;
             if (a.raw_scores) a.raw_scores[o] = fv;
+            if (a.prod_ids) a.prod_ids[o] = i0 * a.n1 + i1;
         }
     }
     }

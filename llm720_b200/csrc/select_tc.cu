@@ -90,7 +90,7 @@ struct SelTcParams {
     int64_t rows;                             // T * H
     int64_t term_rows;                        // row distance between the hi/mid/lo query arrays
     int Q, n0, n1, kp0, kp1, k, mult0, mult1;
-    int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores;
+    int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores; int32_t* prod_ids;
     int* status;
     int32_t* overflow_rows; int* overflow_count;   // rows left to the exact kernel
 };
@@ -437,6 +437,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         if (p.weights) p.weights[o] = w;
                         if (p.ids64) p.ids64[o] = id;
                         if (p.raw_scores) p.raw_scores[o] = fv;
+                        if (p.prod_ids) p.prod_ids[o] = i0 * p.n1 + i1;
                     }
                 }
             }
@@ -503,7 +504,7 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     SelTcParams p;
     p.invn0 = a.invn0; p.invn1 = a.invn1; p.rows = a.rows; p.term_rows = a.term_rows; p.Q = a.Q;
     p.n0 = a.n0; p.n1 = a.n1; p.kp0 = a.kp0; p.kp1 = a.kp1; p.k = a.k; p.mult0 = a.mult0; p.mult1 = a.mult1;
-    p.ids32 = a.ids32; p.weights = a.weights; p.ids64 = a.ids64; p.raw_scores = a.raw_scores; p.status = a.status;
+    p.ids32 = a.ids32; p.weights = a.weights; p.ids64 = a.ids64; p.raw_scores = a.raw_scores; p.prod_ids = a.prod_ids; p.status = a.status;
     p.overflow_rows = a.overflow_rows; p.overflow_count = a.overflow_count;
     const int64_t n_tiles = (a.rows + BM - 1) / BM;
     const unsigned grid = static_cast<unsigned>(n_tiles < a.sm_count ? n_tiles : a.sm_count);

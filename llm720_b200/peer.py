@@ -103,7 +103,7 @@ class PeerOp:
             raise ValueError(f"{name} must be contiguous")
         return t
 
-    def _tensors(self, x, w: dict, out, ids_out=None, scores_out=None, host_io=False) -> _lib.PeerTensors:
+    def _tensors(self, x, w: dict, out, ids_out=None, scores_out=None, host_io=False, product_ids_out=None) -> _lib.PeerTensors:
         a, tb = self.act_dtype, self.table_dtype
         self._dev(x, "x", a, host_ok=host_io)
         self._dev(out, "out", a, host_ok=host_io)
@@ -127,13 +127,16 @@ class PeerOp:
             up_scale=None if w.get("up_scale") is None else w["up_scale"].data_ptr(),
             out=None if out is None else out.data_ptr(),
             ids_out=None if ids_out is None else ids_out.data_ptr(),
-            scores_out=None if scores_out is None else scores_out.data_ptr())
+            scores_out=None if scores_out is None else scores_out.data_ptr(),
+            product_ids_out=None if product_ids_out is None else product_ids_out.data_ptr())
 
     # -- entry points -------------------------------------------------------
-    def forward(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None):
-        """x [T, D] -> out [T, D_out] on the device, asynchronously on the current stream."""
+    def forward(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None, product_ids_out=None):
+        """x [T, D] -> out [T, D_out] on the device, asynchronously on the current stream.  ``product_ids_out``
+        (int32 [T, H, k]) receives the selected experts' true positions in the key grid."""
         T = x.shape[0]
-        t = self._tensors(x, w, out, ids_out, scores_out)
+        self._dev(product_ids_out, "product_ids_out", torch.int32)
+        t = self._tensors(x, w, out, ids_out, scores_out, product_ids_out=product_ids_out)
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_forward(self.handle, C.byref(t), T, _stream(self.device)))
 

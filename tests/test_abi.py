@@ -35,7 +35,7 @@ def test_struct_layouts_match_header():
     assert _lib.PeerConfig.num_experts.offset == 16
     assert _lib.PeerConfig.max_tokens.offset == 80
     assert _lib.PeerConfig.num_key_dims.offset == 88 and _lib.PeerConfig.n_keys3.offset == 96
-    assert C.sizeof(_lib.PeerTensors) == 16 * 8
+    assert C.sizeof(_lib.PeerTensors) == 17 * 8
     assert _lib.PeerTensors.keys2.offset == 14 * 8
 
 
