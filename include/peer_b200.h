@@ -199,6 +199,16 @@ int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_o
                               float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
                               int32_t grad_table_dtype, int64_t n_tokens, void* stream);
 
+/* Backward of the score path: from grad_weights = dL/d(softmax weights) [T, num_heads, top_k] to
+ * grad_queries = dL/d(queries after LayerNorm) [T, num_heads, query_dim] (fp32, written), through the
+ * softmax, the selected scores and the per-slice query normalisation of experts.py:153-163, :327.
+ * queries: the fp32 queries the forward selected from; product_ids: grid positions written by
+ * peer_forward (product_ids_out); scores: the forward's raw scores.  The sub-keys get no gradient,
+ * as in the reference (it reads them through .data, experts.py:154). */
+int peer_select_backward(peer_handle_t h, const float* queries, const void* const* keys,
+                         const int32_t* product_ids, const float* scores, const float* grad_weights,
+                         int64_t n_tokens, float* grad_queries, void* stream);
+
 /* Product-key retrieval (same result as peer_select) for callers that cannot allocate device
  * memory: no handle, no cudaMalloc anywhere on this path.  This entry point has no counterpart in
  * the reference; it exists for embedders that have given all GPU memory to their own pool, or that

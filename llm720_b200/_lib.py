@@ -50,6 +50,8 @@ EXPORTS = {
                               C.c_void_p, C.c_void_p]),
     "peer_select_nd": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int64, C.c_void_p, C.c_void_p,
                                  C.c_void_p]),
+    "peer_select_backward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_void_p, C.c_void_p, C.c_void_p,
+                                       C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_select_noalloc": (C.c_int, [C.POINTER(PeerConfig), C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                                       C.c_void_p, C.c_void_p]),
     "peer_gather_eval": (C.c_int, [C.c_void_p] * 9 + [C.c_int64, C.c_void_p]),

@@ -135,15 +135,13 @@ class _FusedLayer(torch.autograd.Function):
         wanted = [t for t in leaves if t is not None and t.requires_grad]
         got = iter(())
         if wanted:
-            dims, strides = _key_grid(module)
-            pid64 = pid.long()
-            idx = [torch.div(pid64, strides[d], rounding_mode="floor") % dims[d] for d in range(len(dims))]
-            with torch.enable_grad():
+            with torch.enable_grad():                    # projection and LayerNorm again, as torch operations
                 q = F.linear(leaves[0], leaves[1], leaves[2]).float().view(T, H, Q)
                 if leaves[3] is not None:
                     q = F.layer_norm(q, (Q,), leaves[3].float(), None if leaves[4] is None else leaves[4].float(), 1e-5)
-                w2 = torch.softmax(_selected_scores(module, q, idx), dim=-1)
-            got = iter(torch.autograd.grad(w2, wanted, gw.view(T, H, k)))
+            gq = op.select_backward(q.detach().contiguous(), [p.detach() for p in module.sub_keys], pid.view(T, H, k),
+                                    sc, gw.view(T, H, k).contiguous())
+            got = iter(torch.autograd.grad(q, wanted, gq))
         grads = [next(got) if (t is not None and t.requires_grad) else None for t in leaves]
         if need[0]:
             grads[0] = (gx + grads[0].float()).to(x.dtype)

@@ -161,6 +161,22 @@ struct SelectNdArgs {
 };
 cudaError_t launch_select_nd(const SelectNdArgs& a, cudaStream_t s);
 
+// Backward of the selected scores and their softmax with respect to the queries (select_grad.cu)
+struct SelectGradArgs {
+    const float* q_ln;          // [rows, Q] fp32 queries after LayerNorm
+    const void* keys[4];        // [n[d], Q/nd] act dtype, as stored
+    int n[4];
+    long long stride[4];        // true row-major strides of the key grid
+    int nd, Q, k;
+    int norm_keys, norm_query, act_dtype;
+    int64_t rows;
+    const int32_t* prod_ids;    // [rows, k] grid positions of the selected experts
+    const float* scores;        // [rows, k] raw scores of the forward pass
+    const float* grad_weights;  // [rows, k] dL/d softmax weights
+    float* grad_q;              // [rows, Q] written
+};
+cudaError_t launch_select_grad(const SelectGradArgs& a, cudaStream_t s);
+
 // LayerNorm over the model dimension, fp32 parameters (block_ln.cu)
 cudaError_t launch_block_ln(const void* x, int act_dtype, int64_t rows, int D, const float* w, const float* b, float eps,
                             void* out, cudaStream_t s);

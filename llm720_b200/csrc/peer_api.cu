@@ -688,6 +688,32 @@ extern "C" int peer_select_nd(peer_handle_t h, const float* queries, const void*
     return PEER_OK;
 }
 
+extern "C" int peer_select_backward(peer_handle_t h, const float* queries, const void* const* keys,
+                                    const int32_t* product_ids, const float* scores, const float* grad_weights,
+                                    int64_t n_tokens, float* grad_queries, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens == 0) return PEER_OK;
+    if (!queries || !keys || !product_ids || !scores || !grad_weights || !grad_queries)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_select_backward: null pointer");
+    const peer_config_t& c = h->cfg;
+    SelectGradArgs ga{};
+    ga.q_ln = queries;
+    for (int d = 0; d < h->nd; ++d) {
+        if (!keys[d]) return fail(h, PEER_ERR_INVALID_ARG, "sub-key table %d is null", d);
+        ga.keys[d] = keys[d]; ga.n[d] = h->n[d];
+    }
+    ga.stride[h->nd - 1] = 1;
+    for (int d = h->nd - 2; d >= 0; --d) ga.stride[d] = ga.stride[d + 1] * h->n[d + 1];
+    ga.nd = h->nd; ga.Q = c.query_dim; ga.k = c.top_k; ga.norm_keys = c.norm_keys; ga.norm_query = c.norm_query;
+    ga.act_dtype = c.act_dtype; ga.rows = n_tokens * c.num_heads;
+    ga.prod_ids = product_ids; ga.scores = scores; ga.grad_weights = grad_weights; ga.grad_q = grad_queries;
+    cudaError_t e = launch_select_grad(ga, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "score-path backward: this key grid is not implemented");
+    CU_TRY(h, e);
+    h->launches += 1;
+    return PEER_OK;
+}
+
 extern "C" int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* ids, const float* weights,
                                 const void* expert_down, const void* expert_up, const float* down_scale,
                                 const float* up_scale, void* out, int64_t n_tokens, void* stream) {

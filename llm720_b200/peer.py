@@ -217,6 +217,24 @@ class PeerOp:
                                                 _stream(self.device)))
         return ids, sc
 
+    def select_backward(self, queries, keys, product_ids, scores, grad_weights) -> torch.Tensor:
+        """dL/d(queries after LayerNorm) [T, H, Q] fp32 from dL/d(softmax weights) [T, H, k]."""
+        self._dev(queries, "queries", torch.float32)
+        self._dev(product_ids, "product_ids", torch.int32)
+        self._dev(scores, "scores", torch.float32)
+        self._dev(grad_weights, "grad_weights", torch.float32)
+        if len(keys) != self.num_key_dims:
+            raise ValueError(f"{len(keys)} sub-key tables for {self.num_key_dims} key dimensions")
+        for i, kt in enumerate(keys):
+            self._dev(kt, f"keys{i}", self.act_dtype)
+        T = queries.shape[0]
+        gq = torch.empty_like(queries)
+        ptrs = (C.c_void_p * 4)(*[kt.data_ptr() for kt in keys])
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_select_backward(self.handle, _ptr(queries), ptrs, _ptr(product_ids), _ptr(scores),
+                                                      _ptr(grad_weights), T, _ptr(gq), _stream(self.device)))
+        return gq
+
     def gather_eval(self, x, ids32, weights, down, up, down_scale=None, up_scale=None, out=None):
         """out[t] = sum_j weights[t,j] * act(down[ids[t,j]] . x[t]) * up[ids[t,j]]."""
         self._dev(x, "x", self.act_dtype)
