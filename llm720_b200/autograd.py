@@ -63,12 +63,19 @@ class _ExpertEval(torch.autograd.Function):
         x, weights, ids32, down, up = ctx.saved_tensors
         # single-neuron experts of a bf16 layer: the table gradients are summed in bf16, in the buffers that become
         # the parameters' .grad (the reference's bf16 training sums them in bf16 too); otherwise fp32, then cast
-        direct = ctx.op.cfg.expert_hidden_size == 1
+        direct = ctx.op.cfg.expert_hidden_size == 1 and max(down.shape[1], up.shape[1]) * down.element_size() <= 4096
         gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up,
                                                      grad_dtype=down.dtype if direct else torch.float32)
         need = ctx.needs_input_grad
         return (gx.to(x.dtype) if need[0] else None, gw if need[1] else None, None,
                 gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None)
+
+
+def _sums_in_table_dtype(module, table) -> bool:
+    """Single-neuron experts with rows of at most 4 KB: the gradient kernel sums straight into a table of the
+    parameters' dtype.  Otherwise fp32 sums and a cast."""
+    return (module.expert_hidden_size == 1 and
+            max(module.input_dim, module.output_dim) * table.element_size() <= 4096)
 
 
 def _key_grid(module):
@@ -126,7 +133,7 @@ class _FusedLayer(torch.autograd.Function):
         H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
         need = ctx.needs_input_grad
         weights = torch.softmax(sc, dim=-1).view(T, H * k)
-        direct = module.expert_hidden_size == 1
+        direct = _sums_in_table_dtype(module, down)
         gx, gw, gd, gu = op.gather_eval_backward(x, grad_out.contiguous(), ids.view(T, H * k).to(torch.int32), weights,
                                                  down, up, grad_dtype=down.dtype if direct else torch.float32)
         # score path: d(loss)/d(weights) = gw, pushed through softmax, the selected scores and the query path

@@ -796,8 +796,14 @@ extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const v
     g.T = n_tokens; g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
     g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.grad_dtype = grad_table_dtype;
-    cudaError_t e = h->hidden > 1 ? launch_gather_hidden_grad(g, static_cast<cudaStream_t>(stream))
-                                  : launch_gather_grad(g, static_cast<cudaStream_t>(stream));
+    // rows longer than 4 KB do not fit the register-resident kernel: the general kernel takes them (fp32 sums)
+    const int row_bytes = (c.input_dim > c.output_dim ? c.input_dim : c.output_dim) * act_bytes(c.table_dtype);
+    const bool general = h->hidden > 1 || row_bytes > 4096;
+    if (general && grad_table_dtype != PEER_DTYPE_F32)
+        return fail(h, PEER_ERR_UNSUPPORTED, "table gradients of rows longer than 4 KB are accumulated in fp32");
+    if (general && g.hidden < 1) g.hidden = 1;
+    cudaError_t e = general ? launch_gather_hidden_grad(g, static_cast<cudaStream_t>(stream))
+                            : launch_gather_grad(g, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert backward: row width %d/%d is not implemented for this dtype (bf16 up to 2048, fp32 up to 1024)",
                     c.input_dim, c.output_dim);

@@ -259,15 +259,20 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             // mask) without votes or branches, then the lanes append their hits to the
                             // rows' lists side by side.
                             float* slot = s_stage + (s * 32 + lane);
-                            unsigned myhits = 0; int nh = 0;
+                            constexpr uint32_t SLOT_STEP = SCAN_WARPS * 32 * 4;          // bytes between a lane's slots
+                            uint32_t addr = smem_u32(slot);
+                            const uint32_t last = addr + (STAGE_CAP - 1) * SLOT_STEP;
+                            unsigned myhits = 0;
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
                                 const float x = __uint_as_float(r[j]) * sc;
-                                const bool hit = x >= bnd[j];
-                                if (hit) slot[min(nh, STAGE_CAP - 1) * (SCAN_WARPS * 32)] = x;
-                                nh += hit ? 1 : 0;
-                                myhits |= hit ? (1u << j) : 0u;
+                                if (x >= bnd[j]) {                       // three predicated instructions, no branch
+                                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(x) : "memory");
+                                    addr = min(addr + SLOT_STEP, last);
+                                    myhits |= 1u << j;
+                                }
                             }
+                            const int nh = __popc(myhits);
                             int taken = 0;
                             while (__any_sync(FULL_MASK, myhits != 0)) {
                                 if (myhits) {

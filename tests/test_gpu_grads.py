@@ -47,7 +47,7 @@ def _dense_reference(x, ids, w, down, up, act):
 @pytest.mark.parametrize("dtype,D,Dout,H,k,N,T,act", [
     (torch.float32, 32, 48, 2, 4, 64, 7, "gelu"), (torch.float32, 256, 256, 4, 8, 300, 65, "relu"),
     (torch.float32, 1024, 512, 2, 4, 128, 33, "gelu"), (torch.bfloat16, 2048, 2048, 8, 16, 4096, 40, "gelu"),
-    (torch.bfloat16, 512, 1024, 4, 8, 50, 129, "relu")])
+    (torch.bfloat16, 512, 1024, 4, 8, 50, 129, "relu"), (torch.bfloat16, 4096, 4096, 2, 4, 64, 9, "gelu")])
 def test_expert_stage_backward_from_given_selections(cuda_device, dtype, D, Dout, H, k, N, T, act):
     g = torch.Generator(device="cpu").manual_seed(D + T)
     cfg = syn.PeerConfig("t", D, Dout, H, 32, (N, 1), k, dtype, dtype, 1, T)
