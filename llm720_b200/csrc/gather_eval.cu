@@ -27,11 +27,11 @@ constexpr int MAX_SMEM = 227 * 1024;
 
 // Warps per CTA (one CTA per SM) and ring bytes per warp.  Rows of a 16-bit or 32-bit table keep the memory
 // system busy with 8 warps; FP8 rows carry half the bytes per decoded element, so that instance is bound by
-// instruction issue and runs 12 warps with smaller rings and packed activations.
+// instruction issue and runs 14 warps with smaller rings and packed f16 activations (127 registers).
 template <typename TT, int CH> struct WarpCfg {
     static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 12 warps
-    static constexpr int WARPS = MANY ? 12 : 8;
-    static constexpr int RING_BYTES = MANY ? 16 * 1024 : 24 * 1024;
+    static constexpr int WARPS = MANY ? 14 : 8;
+    static constexpr int RING_BYTES = MANY ? 12 * 1024 : 24 * 1024;
 };
 
 template <typename TT, int CH> struct RingCfg {
@@ -108,6 +108,34 @@ template <> struct XIo<__nv_bfloat16, 16> {
     }
 };
 
+// Dot product of 4 e4m3 values (one 32-bit word) with 4 f16 activations (two f16x2 words), accumulated in
+// fp32 by mixed-precision FMAs: every product of two f16 values is exact in fp32, so the result is what the
+// fp32 path computes, without widening the table values first.
+__device__ __forceinline__ void dot4_e4m3_f16(uint32_t w, uint32_t x01, uint32_t x23, float& d0, float& d1) {
+    asm("{\n\t"
+        ".reg .b16 lo, hi;\n\t"
+        ".reg .b32 h01, h23;\n\t"
+        ".reg .f16 a0, a1, a2, a3, b0, b1, b2, b3;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 h01, lo;\n\t"
+        "cvt.rn.f16x2.e4m3x2 h23, hi;\n\t"
+        "mov.b32 {a0, a1}, h01;\n\t"
+        "mov.b32 {a2, a3}, h23;\n\t"
+        "mov.b32 {b0, b1}, %3;\n\t"
+        "mov.b32 {b2, b3}, %4;\n\t"
+        "fma.rn.f32.f16 %0, a0, b0, %0;\n\t"
+        "fma.rn.f32.f16 %1, a1, b1, %1;\n\t"
+        "fma.rn.f32.f16 %0, a2, b2, %0;\n\t"
+        "fma.rn.f32.f16 %1, a3, b3, %1;\n\t"
+        "}"
+        : "+f"(d0), "+f"(d1)
+        : "r"(w), "r"(x01), "r"(x23));
+}
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+    const __half2 v = __floats2half2_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 struct GatherParams {
     const void* x; const int32_t* ids; const float* weights;
     const char* down; const char* up; const float* down_scale; const float* up_scale;
@@ -174,6 +202,10 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
         // The activation row stays in registers for the whole token: fp32, or (rows longer than 64
         // elements per lane, bf16 activations) as packed bf16 pairs widened at each use.
         constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH>::MANY && sizeof(XT) == 2);
+        // FP8 rows: the activations are kept as f16 pairs, scaled by a power of two so
+        // that the row's largest magnitude lies in [1, 2) (a bf16 value then converts exactly unless it is more
+        // than 2^14 times smaller than the largest), and the down-row dot product runs on mixed-precision FMAs.
+        constexpr bool F16X = sizeof(TT) == 1 && sizeof(XT) == 2;
         static_assert(!PACKX || sizeof(XT) == 2, "long rows need bf16 activations");
         float xr[PACKX ? 1 : CH * EPC];
         uint32_t xp[PACKX ? CH * EPC / 2 : 1];
@@ -195,6 +227,20 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
                     for (int e = 0; e < EPC; ++e) xr[i * EPC + e] = 0.f;
                 }
             }
+        }
+        float x_unscale = 1.0f;
+        if constexpr (F16X) {
+            float mx = 0.f;
+#pragma unroll
+            for (int i = 0; i < CH * EPC / 2; ++i) mx = fmaxf(mx, fmaxf(fabsf(bf16_lo(xp[i])), fabsf(bf16_hi(xp[i]))));
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(FULL_MASK, mx, o));
+            const int ex = (__float_as_int(mx) >> 23) & 0xff;                 // biased exponent of the largest magnitude
+            const bool usable = ex > 0 && ex < 254;                            // zero row, or inf/nan: leave the scale at 1
+            const float sc = usable ? __int_as_float((254 - ex) << 23) : 1.0f; // 2^-(ex-127)
+            x_unscale = usable ? __int_as_float(ex << 23) : 1.0f;              // 2^(ex-127)
+#pragma unroll
+            for (int i = 0; i < CH * EPC / 2; ++i) xp[i] = pack_f16(bf16_lo(xp[i]) * sc, bf16_hi(xp[i]) * sc);
         }
         auto xval = [&](int idx) -> float {
             if constexpr (PACKX) return (idx & 1) ? bf16_hi(xp[idx >> 1]) : bf16_lo(xp[idx >> 1]);
@@ -236,12 +282,20 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
                     const int c = lane + 32 * i;
                     if (c < p.nch_u) {
                         const uint4 raw = *reinterpret_cast<const uint4*>(rb + c * 16);
-                        float f[EPC];
-                        Chunk<TT>::decode(raw, f);
+                        if constexpr (F16X) {
+                            const uint32_t* xw = xp + i * EPC / 2;          // 8 f16x2 words for this chunk's 16 elements
+                            dot4_e4m3_f16(raw.x, xw[0], xw[1], d0, d1);
+                            dot4_e4m3_f16(raw.y, xw[2], xw[3], d0, d1);
+                            dot4_e4m3_f16(raw.z, xw[4], xw[5], d0, d1);
+                            dot4_e4m3_f16(raw.w, xw[6], xw[7], d0, d1);
+                        } else {
+                            float f[EPC];
+                            Chunk<TT>::decode(raw, f);
 #pragma unroll
-                        for (int q = 0; q < EPC; q += 2) {
-                            d0 = fmaf(f[q], xval(i * EPC + q), d0);
-                            d1 = fmaf(f[q + 1], xval(i * EPC + q + 1), d1);
+                            for (int q = 0; q < EPC; q += 2) {
+                                d0 = fmaf(f[q], xval(i * EPC + q), d0);
+                                d1 = fmaf(f[q + 1], xval(i * EPC + q + 1), d1);
+                            }
                         }
                     }
                 }
@@ -250,6 +304,7 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
             if (lane == 0 && 2 * e + STAGES < total_rows) issue(2 * e + STAGES, slot);
             if (++slot == STAGES) { slot = 0; parity ^= 1; }
             float dot = warp_sum(d0 + d1);
+            if constexpr (F16X) dot *= x_unscale;
             if (SCALED) dot *= s_us[e];
             float g = p.activation == PEER_ACT_GELU ? gelu_erf(dot) : fmaxf(dot, 0.f);
             g *= s_w[e];
