@@ -30,7 +30,7 @@ constexpr int MAX_SMEM = 227 * 1024;
 // instruction issue and runs 14 warps with smaller rings and packed f16 activations (127 registers).
 template <typename TT, int CH> struct WarpCfg {
     static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 12 warps
-    static constexpr int WARPS = MANY ? 16 : 8;
+    static constexpr int WARPS = MANY ? 14 : 8;
     static constexpr int RING_BYTES = MANY ? 12 * 1024 : 24 * 1024;
 };
 
