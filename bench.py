@@ -39,7 +39,8 @@ FALLBACK_HBM_GBS = 6650.0
 # case of the same kernel (4096 tokens, 262,144 experts; dram__bytes_read.sum + dram__bytes_write.sum =
 # 4.150 GB for 4.295 GB of algorithmic bytes; profiles/gather_eval_bf16_d2048_small_case.md).  Traffic
 # grows in proportion to the tokens, so the bench scales it to its own launch size.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bfloat16": 0.966}
+# FP8 tables: 2.147 GB read + 0.02 GB written for 2.152 GB algorithmic (profiles/gather_eval_fp8_d2048_small_case.md).
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"bfloat16": 0.966, "float8_e4m3fn": 1.007}
 
 
 def parse():

@@ -58,6 +58,24 @@ template <> struct Chunk16<__nv_bfloat16> {
     }
 };
 
+// sum of the 8 products of two 16-byte chunks of bf16 values, added to d: mixed-precision FMAs take the bf16
+// operands as they are stored (a bf16 x bf16 product is exact in fp32, so this equals widening first)
+__device__ __forceinline__ void dot8_bf16(const uint4& a, const uint4& b, float& d) {
+    asm("{\n\t"
+        ".reg .b16 a0, a1, b0, b1;\n\t"
+        "mov.b32 {a0, a1}, %1;\n\tmov.b32 {b0, b1}, %5;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %0, a1, b1, %0;\n\t"
+        "mov.b32 {a0, a1}, %2;\n\tmov.b32 {b0, b1}, %6;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %0, a1, b1, %0;\n\t"
+        "mov.b32 {a0, a1}, %3;\n\tmov.b32 {b0, b1}, %7;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %0, a1, b1, %0;\n\t"
+        "mov.b32 {a0, a1}, %4;\n\tmov.b32 {b0, b1}, %8;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %0, a1, b1, %0;\n\t"
+        "}"
+        : "+f"(d)
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w));
+}
+
 __device__ __forceinline__ float act_value(float z, int activation) {
     return activation == PEER_ACT_GELU ? gelu_erf(z) : fmaxf(z, 0.f);
 }
@@ -113,18 +131,23 @@ __global__ void __launch_bounds__(THREADS) gather_grad_kernel(const GradParams p
 #pragma unroll
             for (int i = 0; i < CH; ++i) {
                 const int c = lane + 32 * i;
-                float a[EPC], b[EPC];
-                if (c < p.nch_u) {
-                    Chunk16<XT>::decode(__ldg(ur + c), a);
-                    Chunk16<XT>::decode(xc[i], b);
+                if constexpr (sizeof(XT) == 2) {
+                    if (c < p.nch_u) dot8_bf16(__ldg(ur + c), xc[i], z);
+                    if (c < p.nch_v) dot8_bf16(__ldg(vr + c), dyc[i], g);
+                } else {
+                    float a[EPC], b[EPC];
+                    if (c < p.nch_u) {
+                        Chunk16<XT>::decode(__ldg(ur + c), a);
+                        Chunk16<XT>::decode(xc[i], b);
 #pragma unroll
-                    for (int q = 0; q < EPC; ++q) z = fmaf(a[q], b[q], z);
-                }
-                if (c < p.nch_v) {
-                    Chunk16<XT>::decode(__ldg(vr + c), a);
-                    Chunk16<XT>::decode(dyc[i], b);
+                        for (int q = 0; q < EPC; ++q) z = fmaf(a[q], b[q], z);
+                    }
+                    if (c < p.nch_v) {
+                        Chunk16<XT>::decode(__ldg(vr + c), a);
+                        Chunk16<XT>::decode(dyc[i], b);
 #pragma unroll
-                    for (int q = 0; q < EPC; ++q) g = fmaf(a[q], b[q], g);
+                        for (int q = 0; q < EPC; ++q) g = fmaf(a[q], b[q], g);
+                    }
                 }
             }
             z = warp_sum(z);
