@@ -7,9 +7,11 @@
 //
 // One CTA tile = 128 tokens x one head (N = query_dim <= 256), K walked in
 // 64-column TMA boxes through a 4-stage mbarrier ring.  Warp 0 issues the TMA
-// loads, warp 1 the MMAs, warps 2-5 own one TMEM lane (= one token row) each
-// and run the epilogue; two accumulators alternate so the epilogue of a tile
-// overlaps the MMAs of the next.  The grid is persistent.
+// loads, warp 1 the MMAs, warps 2-9 run the epilogue: a thread owns one TMEM
+// lane (= one token row) and one half of the head's columns (= one query
+// half), the two threads of a row exchange their LayerNorm partial sums through
+// shared memory; two accumulators alternate so the epilogue of a tile overlaps
+// the MMAs of the next.  The grid is persistent.
 //
 // Output: the normalised query halves split into three bf16 terms
 // (hi + mid + lo = the fp32 value to 2^-27), the form the select kernel feeds
@@ -27,8 +29,8 @@ constexpr int STAGES = 4;
 constexpr int MAXQ = 256;
 constexpr int A_BYTES = BM * BK * 2;        // 16 KB
 constexpr int B_BYTES = MAXQ * BK * 2;      // 32 KB
-constexpr int THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int THREADS = 320;
+constexpr int EPI_THREADS = 256;
 constexpr float LN_EPS = 1e-5f;
 constexpr float NORM_EPS = 1e-12f;
 constexpr uint32_t TMEM_COLS = 512;
@@ -37,7 +39,8 @@ struct SmemLayout {
     static constexpr size_t a_off = 0;
     static constexpr size_t b_off = a_off + static_cast<size_t>(STAGES) * A_BYTES;
     static constexpr size_t par_off = b_off + static_cast<size_t>(STAGES) * B_BYTES;   // bias[2][256], gamma[256], beta[256]
-    static constexpr size_t bar_off = par_off + 4 * MAXQ * sizeof(float);
+    static constexpr size_t red_off = par_off + 4 * MAXQ * sizeof(float);             // LayerNorm partial sums [2][2][128]
+    static constexpr size_t bar_off = red_off + 4 * BM * sizeof(float);
     static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 16 + 1024;   // + slack to align the base to 1024
 };
 
@@ -57,6 +60,7 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     float* s_bias = reinterpret_cast<float*>(smem + SmemLayout::par_off);       // [2][MAXQ]
     float* s_gamma = s_bias + 2 * MAXQ;
     float* s_beta = s_gamma + MAXQ;
+    float* s_red = reinterpret_cast<float*>(smem + SmemLayout::red_off);        // [sum | centred squares][column half][row]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SmemLayout::bar_off);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     const uint32_t sA = smem_u32(smem + SmemLayout::a_off), sB = smem_u32(smem + SmemLayout::b_off);
@@ -133,11 +137,13 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
         }
     } else {
-        // ---------------- epilogue: one thread per token row ----------------
+        // ---------------- epilogue: one thread per (token row, query half) ----------------
         const int quarter = warp & 3;                 // TMEM lane quarter this warp may read
+        const int colhalf = (warp - 2) >> 2;          // which half of the head's columns
         const int row = quarter * 32 + lane;
-        const int et = tid - 64;                      // 0..127
+        const int et = tid - 64;                      // 0..255
         const int nb = Q / 32;
+        const int b_lo = colhalf * (nb / 2), b_hi = b_lo + nb / 2;
         const int half = Q / 2;
         const float invQ = 1.0f / static_cast<float>(Q);
         int acc = 0; uint32_t acc_phase = 0; bool ok = true;
@@ -145,9 +151,13 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int m_blk = static_cast<int>(tile / H), h = static_cast<int>(tile % H);
             float* sb = s_bias + acc * MAXQ;
             for (int c = et; c < Q; c += EPI_THREADS) sb[c] = bias ? __bfloat162float(bias[h * Q + c]) : 0.f;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
             if (ok && !mbar_wait(accf_bar(acc), acc_phase, status)) ok = false;
-            // every epilogue thread takes the same decision so the named barrier above stays matched
+            {   // one barrier publishes the bias and makes the decision the same in every epilogue thread
+                int all_ok;
+                asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.and.pred p, 1, 256, q;\n\t"
+                             "selp.s32 %0, 1, 0, p;\n\t}" : "=r"(all_ok) : "r"(static_cast<int>(ok)) : "memory");
+                ok = all_ok != 0;
+            }
             if (!ok) continue;
             tc::fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * MAXQ;
@@ -155,15 +165,17 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             float mean = 0.f, rstd = 1.f;
             if (layer_norm) {
                 float s = 0.f;
-                for (int b = 0; b < nb; ++b) {
+                for (int b = b_lo; b < b_hi; ++b) {
                     tc::tmem_ld32(taddr + b * 32, r);
                     tc::tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j) s += __uint_as_float(r[j]) + sb[b * 32 + j];
                 }
-                mean = s * invQ;
+                s_red[colhalf * BM + row] = s;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                mean = (s_red[row] + s_red[BM + row]) * invQ;
                 float ss = 0.f;
-                for (int b = 0; b < nb; ++b) {
+                for (int b = b_lo; b < b_hi; ++b) {
                     tc::tmem_ld32(taddr + b * 32, r);
                     tc::tmem_ld_wait();
 #pragma unroll
@@ -172,14 +184,16 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                         ss = fmaf(d, d, ss);
                     }
                 }
-                rstd = 1.0f / sqrtf(ss * invQ + LN_EPS);
+                s_red[2 * BM + colhalf * BM + row] = ss;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                rstd = 1.0f / sqrtf((s_red[2 * BM + row] + s_red[3 * BM + row]) * invQ + LN_EPS);
             }
             float n0 = 1.f, n1 = 1.f;
             const int64_t grow = static_cast<int64_t>(m_blk) * BM + row;
             const int64_t obase = (grow * H + h) * Q;
             {
                 float s0 = 0.f, s1 = 0.f;
-                for (int b = 0; b < nb; ++b) {
+                for (int b = b_lo; b < b_hi; ++b) {
                     tc::tmem_ld32(taddr + b * 32, r);
                     tc::tmem_ld_wait();
                     float y[32];
@@ -203,7 +217,7 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (norm_query) { n0 = fmaxf(sqrtf(s0), NORM_EPS); n1 = fmaxf(sqrtf(s1), NORM_EPS); }
             }
             if (q_hat_out || split_out) {
-                for (int b = 0; b < nb; ++b) {
+                for (int b = b_lo; b < b_hi; ++b) {
                     tc::tmem_ld32(taddr + b * 32, r);
                     tc::tmem_ld_wait();
                     const float nn = (b * 32 < half) ? n0 : n1;
