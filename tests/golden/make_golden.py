@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <reference checkout>
 
 For every case the reference ``PEER`` (llm/models/experts.py) is built, loaded
 with seeded synthetic weights and run on CPU in fp32; the oracle restatement
@@ -113,7 +113,8 @@ def run_case(PEER, name, cfg, seed, random_affine, table_rows, store_weights):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.path.join(os.path.dirname(ROOT), "reference"),
+                    help="checkout of the reference project (default: a directory named reference next to this repository)")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from llm.models.experts import PEER  # the reference, unmodified

@@ -3,7 +3,7 @@ the benchmark shape: several neurons per expert and key grids of one, three and 
 (the layers the reference's own tests build, tests/test_peer_integration.py:24-111,
 tests/test_peer_selection.py:53-72).
 
-    python tests/golden/make_golden_general.py --reference /root/reference
+    python tests/golden/make_golden_general.py --reference <reference checkout>
 
 Each case: reference ``PEER`` in fp32 on CPU with seeded synthetic weights; forward in both the
 module call and ``_get_expert_indices_pytorch``; backward with a seeded grad_out.  The oracle
@@ -96,7 +96,8 @@ def run_case(PEER, name):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.path.join(os.path.dirname(ROOT), "reference"),
+                    help="checkout of the reference project (default: a directory named reference next to this repository)")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from llm.models.experts import PEER  # the reference, unmodified

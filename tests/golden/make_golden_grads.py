@@ -1,6 +1,6 @@
 """Generate golden GRADIENTS from the reference module itself.
 
-    python tests/golden/make_golden_grads.py --reference /root/reference
+    python tests/golden/make_golden_grads.py --reference <reference checkout>
 
 For every case the reference ``PEER`` (llm/models/experts.py) is built in fp32
 with seeded synthetic weights, run on CPU with autograd, and ``out`` is
@@ -83,7 +83,8 @@ def run_case(PEER, name, cfg, seed, random_affine):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.path.join(os.path.dirname(ROOT), "reference"),
+                    help="checkout of the reference project (default: a directory named reference next to this repository)")
     a = ap.parse_args()
     sys.path.insert(0, a.reference)
     from llm.models.experts import PEER  # the reference, unmodified

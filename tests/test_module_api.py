@@ -32,9 +32,14 @@ def test_constructor_signature_matches_reference():
     assert list(names[1:]) == [n for n, _ in REF_SIGNATURE]
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/llm"), reason="reference checkout not present")
+# a checkout of the reference project next to this repository (or named by LLM720_REFERENCE), when there is one
+REFERENCE_DIR = os.environ.get("LLM720_REFERENCE") or os.path.join(
+    os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_DIR, "llm")), reason="reference checkout not present")
 def test_signature_and_state_dict_against_the_reference_itself():
-    sys.path.insert(0, "/root/reference")
+    sys.path.insert(0, REFERENCE_DIR)
     from llm.models.experts import PEER as RefPEER
     flat = lambda f: [(n, p.default, p.kind) for n, p in inspect.signature(f).parameters.items()]
     assert flat(RefPEER.__init__) == flat(PEER.__init__)
