@@ -35,7 +35,7 @@ enum {
     PEER_ERR_BOUNDS = 5         /* an expert id outside [0, num_experts) was seen    */
 };
 
-enum { PEER_DTYPE_F32 = 0, PEER_DTYPE_BF16 = 1, PEER_DTYPE_E4M3 = 2 };
+enum { PEER_DTYPE_F32 = 0, PEER_DTYPE_BF16 = 1, PEER_DTYPE_E4M3 = 2, PEER_DTYPE_F16 = 3 };
 enum { PEER_ACT_GELU = 0, PEER_ACT_RELU = 1 };
 /* How the two per-dimension sub-key indices (i0, i1) become a flat expert id.
  * REFERENCE: i0 + i1, what llm/models/experts.py:203-230 computes (the first
@@ -58,8 +58,9 @@ typedef struct peer_config {
                                    [h, input_dim] blocks, up rows [output_dim, h] blocks)           */
     int32_t activation;         /* PEER_ACT_*                                         */
     int32_t norm_keys, norm_query, layer_norm; /* booleans (batch_norm_query = layer_norm) */
-    int32_t act_dtype;          /* dtype of x, out, query weights, LN affine, sub-keys: F32 or BF16 */
-    int32_t table_dtype;        /* dtype of expert_down / expert_up: F32, BF16 or E4M3 */
+    int32_t act_dtype;          /* dtype of x, out, query weights, LN affine, sub-keys: F32, BF16 or F16 */
+    int32_t table_dtype;        /* dtype of expert_down / expert_up: F32, BF16, E4M3 (with BF16 activations)
+                                   or F16 (with F16 activations; fp16 layers run the CUDA-core kernels) */
     int32_t index_mode;         /* PEER_INDEX_*                                       */
     int64_t max_tokens;         /* scratch capacity; longer inputs are processed in slices */
     int32_t num_key_dims;       /* len(product_key_dim): 1..4; 0 is read as 2         */

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libpeer_b200.so")
 
 ABI_VERSION = 2
 OK, ERR_INVALID_ARG, ERR_UNSUPPORTED, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_BOUNDS = range(6)
-DTYPE_F32, DTYPE_BF16, DTYPE_E4M3 = 0, 1, 2
+DTYPE_F32, DTYPE_BF16, DTYPE_E4M3, DTYPE_F16 = 0, 1, 2, 3
 ACT_GELU, ACT_RELU = 0, 1
 INDEX_REFERENCE, INDEX_PRODUCT = 0, 1
 

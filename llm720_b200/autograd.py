@@ -63,7 +63,8 @@ class _ExpertEval(torch.autograd.Function):
         x, weights, ids32, down, up = ctx.saved_tensors
         # single-neuron experts of a bf16 layer: the table gradients are summed in bf16, in the buffers that become
         # the parameters' .grad (the reference's bf16 training sums them in bf16 too); otherwise fp32, then cast
-        direct = ctx.op.cfg.expert_hidden_size == 1 and max(down.shape[1], up.shape[1]) * down.element_size() <= 4096
+        direct = (ctx.op.cfg.expert_hidden_size == 1 and down.dtype != torch.float16 and
+                  max(down.shape[1], up.shape[1]) * down.element_size() <= 4096)
         gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up,
                                                      grad_dtype=down.dtype if direct else torch.float32)
         need = ctx.needs_input_grad
@@ -74,7 +75,7 @@ class _ExpertEval(torch.autograd.Function):
 def _sums_in_table_dtype(module, table) -> bool:
     """Single-neuron experts with rows of at most 4 KB: the gradient kernel sums straight into a table of the
     parameters' dtype.  Otherwise fp32 sums and a cast."""
-    return (module.expert_hidden_size == 1 and
+    return (module.expert_hidden_size == 1 and table.dtype != torch.float16 and
             max(module.input_dim, module.output_dim) * table.element_size() <= 4096)
 
 

@@ -42,6 +42,8 @@ cudaError_t launch_block_ln(const void* x, int act_dtype, int64_t rows, int D, c
     else if (act_dtype == PEER_DTYPE_BF16)
         block_ln_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), w, b, eps, rows, D,
                                                               static_cast<__nv_bfloat16*>(out));
+    else if (act_dtype == PEER_DTYPE_F16)
+        block_ln_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(x), w, b, eps, rows, D, static_cast<__half*>(out));
     else
         return cudaErrorInvalidValue;
     return cudaGetLastError();

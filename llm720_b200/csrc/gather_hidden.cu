@@ -185,6 +185,9 @@ cudaError_t launch_gather_hidden(const GatherArgs& a, cudaStream_t s) {
     } else if (a.act_dtype == PEER_DTYPE_BF16) {
         if ((e = opt_in(gather_hidden_kernel<__nv_bfloat16>, smem)) != cudaSuccess) return e;
         gather_hidden_kernel<__nv_bfloat16><<<grid_for(a.T, a.sm_count), THREADS, smem, s>>>(a);
+    } else if (a.act_dtype == PEER_DTYPE_F16) {
+        if ((e = opt_in(gather_hidden_kernel<__half>, smem)) != cudaSuccess) return e;
+        gather_hidden_kernel<__half><<<grid_for(a.T, a.sm_count), THREADS, smem, s>>>(a);
     } else {
         return cudaErrorInvalidValue;
     }
@@ -203,6 +206,9 @@ cudaError_t launch_gather_hidden_grad(const GatherGradArgs& a, cudaStream_t s) {
     } else if (a.act_dtype == PEER_DTYPE_BF16) {
         if ((e = opt_in(gather_hidden_grad_kernel<__nv_bfloat16>, smem)) != cudaSuccess) return e;
         gather_hidden_grad_kernel<__nv_bfloat16><<<grid_for(a.T, a.sm_count), THREADS, smem, s>>>(a);
+    } else if (a.act_dtype == PEER_DTYPE_F16) {
+        if ((e = opt_in(gather_hidden_grad_kernel<__half>, smem)) != cudaSuccess) return e;
+        gather_hidden_grad_kernel<__half><<<grid_for(a.T, a.sm_count), THREADS, smem, s>>>(a);
     } else {
         return cudaErrorInvalidValue;
     }

@@ -86,7 +86,7 @@ namespace peer {
 void set_global_error(const char* msg) { g_create_error = msg ? msg : ""; }
 }  // namespace peer
 
-static int act_bytes(int dt) { return dt == PEER_DTYPE_F32 ? 4 : (dt == PEER_DTYPE_BF16 ? 2 : 1); }
+static int act_bytes(int dt) { return dt == PEER_DTYPE_F32 ? 4 : ((dt == PEER_DTYPE_BF16 || dt == PEER_DTYPE_F16) ? 2 : 1); }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // k' of the reference (llm/models/experts.py:168-187).
@@ -143,12 +143,13 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     const int nkeys[4] = {c->n_keys0, nd > 1 ? c->n_keys1 : 1, nd > 2 ? c->n_keys2 : 1, nd > 3 ? c->n_keys3 : 1};
     if (c->activation != PEER_ACT_GELU && c->activation != PEER_ACT_RELU)
         return fail(nullptr, PEER_ERR_UNSUPPORTED, "activation %d is not implemented", c->activation);
-    if (c->act_dtype != PEER_DTYPE_F32 && c->act_dtype != PEER_DTYPE_BF16)
-        return fail(nullptr, PEER_ERR_UNSUPPORTED, "act_dtype must be fp32 or bf16");
+    if (c->act_dtype != PEER_DTYPE_F32 && c->act_dtype != PEER_DTYPE_BF16 && c->act_dtype != PEER_DTYPE_F16)
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "act_dtype must be fp32, bf16 or fp16");
     const bool combo = (c->act_dtype == PEER_DTYPE_F32 && c->table_dtype == PEER_DTYPE_F32) ||
+                       (c->act_dtype == PEER_DTYPE_F16 && c->table_dtype == PEER_DTYPE_F16) ||
                        (c->act_dtype == PEER_DTYPE_BF16 && (c->table_dtype == PEER_DTYPE_BF16 || c->table_dtype == PEER_DTYPE_E4M3));
     if (!combo)
-        return fail(nullptr, PEER_ERR_UNSUPPORTED, "unsupported dtype pair: act %d, table %d (fp32/fp32, bf16/bf16, bf16/e4m3)",
+        return fail(nullptr, PEER_ERR_UNSUPPORTED, "unsupported dtype pair: act %d, table %d (fp32/fp32, bf16/bf16, bf16/e4m3, fp16/fp16)",
                     c->act_dtype, c->table_dtype);
     if (c->input_dim <= 0 || c->output_dim <= 0 || c->num_heads <= 0 || c->top_k <= 0 || nkeys[0] <= 0 ||
         nkeys[1] <= 0 || nkeys[2] <= 0 || nkeys[3] <= 0 || c->query_dim <= 0 || c->max_tokens <= 0)
@@ -420,7 +421,9 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
     g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.residual = residual;
-    cudaError_t e = h->hidden > 1 ? launch_gather_hidden(g, s) : launch_gather_eval(g, s);
+    const bool general_rows = h->hidden > 1 || c.act_dtype == PEER_DTYPE_F16;     // fp16 layers: the general kernel
+    if (general_rows && g.hidden < 1) g.hidden = 1;
+    cudaError_t e = general_rows ? launch_gather_hidden(g, s) : launch_gather_eval(g, s);
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
                     c.input_dim, c.output_dim, g.HK);
@@ -732,8 +735,10 @@ extern "C" int peer_gather_eval(peer_handle_t h, const void* x, const int32_t* i
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
     g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden;
-    cudaError_t e = h->hidden > 1 ? launch_gather_hidden(g, static_cast<cudaStream_t>(stream))
-                                  : launch_gather_eval(g, static_cast<cudaStream_t>(stream));
+    const bool general_rows = h->hidden > 1 || c.act_dtype == PEER_DTYPE_F16;
+    if (general_rows && g.hidden < 1) g.hidden = 1;
+    cudaError_t e = general_rows ? launch_gather_hidden(g, static_cast<cudaStream_t>(stream))
+                                 : launch_gather_eval(g, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
                     c.input_dim, c.output_dim, g.HK);
@@ -751,8 +756,8 @@ extern "C" int peer_gather_eval_partial(peer_handle_t h, const void* x, const in
     const peer_config_t& c = h->cfg;
     if (!x || !ids || !weights || !counts || !expert_down || !expert_up || !out_f32)
         return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_partial: null pointer");
-    if (h->hidden > 1)
-        return fail(h, PEER_ERR_UNSUPPORTED, "peer_gather_eval_partial: experts with several neurons are not implemented");
+    if (h->hidden > 1 || c.act_dtype == PEER_DTYPE_F16)
+        return fail(h, PEER_ERR_UNSUPPORTED, "peer_gather_eval_partial: experts with several neurons and fp16 layers are not implemented");
     if (entries_per_token <= 0 || n_local_rows <= 0 || n_local_rows > c.num_experts)
         return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_partial: entries_per_token and n_local_rows must be positive, rows <= num_experts");
     if (c.table_dtype == PEER_DTYPE_E4M3 && (!down_scale || !up_scale))
@@ -798,7 +803,7 @@ extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const v
     g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.grad_dtype = grad_table_dtype;
     // rows longer than 4 KB do not fit the register-resident kernel: the general kernel takes them (fp32 sums)
     const int row_bytes = (c.input_dim > c.output_dim ? c.input_dim : c.output_dim) * act_bytes(c.table_dtype);
-    const bool general = h->hidden > 1 || row_bytes > 4096;
+    const bool general = h->hidden > 1 || row_bytes > 4096 || c.act_dtype == PEER_DTYPE_F16;
     if (general && grad_table_dtype != PEER_DTYPE_F32)
         return fail(h, PEER_ERR_UNSUPPORTED, "table gradients of rows longer than 4 KB are accumulated in fp32");
     if (general && g.hidden < 1) g.hidden = 1;

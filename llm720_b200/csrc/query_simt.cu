@@ -31,6 +31,14 @@ __device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, flo
     v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
 }
 
+template <>
+__device__ __forceinline__ void load4<__half>(const __half* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
 // One CTA: BM tokens x one head.  Warp w owns token rows w*8..w*8+7 whole
 // (columns lane + 32*j), so the LayerNorm and the half norms are warp
 // reductions and nothing is staged through shared memory.
@@ -217,8 +225,9 @@ cudaError_t launch_query_t(const QueryArgs& a, cudaStream_t s) {
 
 cudaError_t launch_query_simt(const QueryArgs& a, cudaStream_t s) {
     if (a.T == 0) return cudaSuccess;
-    return a.act_dtype == PEER_DTYPE_F32 ? launch_query_t<float>(a, s)
-                                         : launch_query_t<__nv_bfloat16>(a, s);
+    if (a.act_dtype == PEER_DTYPE_F32) return launch_query_t<float>(a, s);
+    if (a.act_dtype == PEER_DTYPE_F16) return launch_query_t<__half>(a, s);
+    return launch_query_t<__nv_bfloat16>(a, s);
 }
 
 cudaError_t launch_normalize_rows(const void* in, int in_dtype, int64_t rows, int width, int do_norm,
@@ -228,6 +237,9 @@ cudaError_t launch_normalize_rows(const void* in, int in_dtype, int64_t rows, in
     if (in_dtype == PEER_DTYPE_F32)
         normalize_rows_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(in), rows, width,
                                                             do_norm, transpose_out, out);
+    else if (in_dtype == PEER_DTYPE_F16)
+        normalize_rows_kernel<__half><<<blocks, 256, 0, s>>>(static_cast<const __half*>(in), rows, width, do_norm,
+                                                             transpose_out, out);
     else
         normalize_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(
             static_cast<const __nv_bfloat16*>(in), rows, width, do_norm, transpose_out, out);

@@ -91,6 +91,7 @@ cudaError_t launch_select_grad(const SelectGradArgs& a, cudaStream_t s) {
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (a.act_dtype == PEER_DTYPE_F32) select_grad_kernel<float><<<static_cast<unsigned>(blocks), WARPS * 32, 0, s>>>(a);
     else if (a.act_dtype == PEER_DTYPE_BF16) select_grad_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), WARPS * 32, 0, s>>>(a);
+    else if (a.act_dtype == PEER_DTYPE_F16) select_grad_kernel<__half><<<static_cast<unsigned>(blocks), WARPS * 32, 0, s>>>(a);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }

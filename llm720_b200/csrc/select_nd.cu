@@ -181,6 +181,7 @@ cudaError_t launch_select_nd(const SelectNdArgs& a, cudaStream_t s) {
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (a.act_dtype == PEER_DTYPE_F32) select_nd_kernel<float><<<static_cast<unsigned>(blocks), THREADS, 0, s>>>(a);
     else if (a.act_dtype == PEER_DTYPE_BF16) select_nd_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), THREADS, 0, s>>>(a);
+    else if (a.act_dtype == PEER_DTYPE_F16) select_nd_kernel<__half><<<static_cast<unsigned>(blocks), THREADS, 0, s>>>(a);
     else return cudaErrorInvalidValue;
     return cudaGetLastError();
 }

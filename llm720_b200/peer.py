@@ -19,7 +19,7 @@ import torch.nn as nn
 from . import _lib
 
 _DT = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16,
-       torch.float8_e4m3fn: _lib.DTYPE_E4M3}
+       torch.float8_e4m3fn: _lib.DTYPE_E4M3, torch.float16: _lib.DTYPE_F16}
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -48,7 +48,7 @@ class PeerOp:
             raise ValueError(f"Unsupported activation: {activation}")
         if index_mode not in ("reference", "product"):
             raise ValueError(f"index_mode={index_mode!r}: 'reference' or 'product'")
-        if act_dtype not in (torch.float32, torch.bfloat16) or table_dtype not in _DT:
+        if act_dtype not in (torch.float32, torch.bfloat16, torch.float16) or table_dtype not in _DT:
             raise ValueError(f"unsupported dtypes: activations {act_dtype}, tables {table_dtype}")
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         if self.device.type != "cuda":

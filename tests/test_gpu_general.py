@@ -114,6 +114,35 @@ def test_reference_test_layer_in_bf16(cuda_device):
     assert l1(m.expert_down.weight.grad.float().cpu(), leaf["expert_down.weight"].grad) <= 2e-2
 
 
+@pytest.mark.parametrize("grid,Q", [((8, 8), 32), ((4, 4, 4), 30)])
+def test_reference_test_layers_in_fp16(cuda_device, grid, Q):
+    """The fp16 layer of the reference's integration test (tests/test_peer_integration.py:46-67) and its 3-D
+    sibling, on the CUDA-core kernels, against the fp32 oracle on the same fp16-representable values."""
+    cfg = syn.PeerConfig("t", 128, 128, 2, Q, grid, 4, torch.float16, torch.float16, 4, 16,
+                         expert_hidden_size=8, batch_norm_query=False)
+    sd = syn.make_weights(cfg, 41, "cpu", random_affine=True)
+    x = syn.make_input(cfg, 41, "cpu")
+    m = _module(cfg, sd, cuda_device)
+    with torch.no_grad():
+        out_i = m(x.to(cuda_device))
+    xl = x.to(cuda_device).requires_grad_(True)
+    out = m(xl)
+    assert out.dtype == torch.float16 and out.shape == (4, 16, 128) and torch.equal(out.detach(), out_i)
+    out.sum().backward()
+    m._op.query_status()
+    leaf = {k: v.float().clone().requires_grad_(True) for k, v in sd.items()}
+    xo = x.float().clone().requires_grad_(True)
+    ref, ref_ids, ref_sc = orc.forward(xo, general_oracle_weights(leaf, cfg), oracle_shape(cfg), "reference")
+    ref.sum().backward()
+    _check_ids(m._last_expert_indices, ref_ids, ref_sc.detach(), m._last_expert_scores)
+    l1 = lambda a, b: float((a - b).abs().sum() / b.abs().sum())
+    assert l1(out.detach().float().cpu(), ref.detach()) <= 2e-3
+    assert l1(xl.grad.float().cpu(), xo.grad) <= 5e-3
+    assert l1(m.query_proj.weight.grad.float().cpu(), leaf["query_proj.weight"].grad) <= 2e-2
+    assert l1(m.expert_up.weight.grad.float().cpu(), leaf["expert_up.weight"].grad) <= 5e-3
+    assert l1(m.expert_down.weight.grad.float().cpu(), leaf["expert_down.weight"].grad) <= 5e-3
+
+
 def test_rejected_shapes_raise(cuda_device):
     with pytest.raises(ValueError):
         PEER(32, 32, 32, product_key_dim=[2, 2, 2, 2, 2])
