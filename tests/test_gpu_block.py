@@ -73,6 +73,21 @@ def test_block_forward_bf16_sliced(cuda_device):
     assert mx <= 3e-2 and l1 <= 1e-3, (mx, l1)
 
 
+@pytest.mark.parametrize("name", ["k3d_h8_fp32", "h8_fp32"])
+def test_block_forward_on_the_general_kernels(cuda_device, name):
+    """Several neurons per expert / a 3-D key grid: the residual is added by the general expert kernel."""
+    from _util import load_general
+    cfg, sd, x, _ = load_general(name)
+    m = _module(cfg, sd, cuda_device)
+    ln = _ln(cfg.input_dim, 3).to(cuda_device)
+    hidden = (x * 2.0 - 0.3).to(cuda_device)
+    with torch.no_grad():
+        out = m.block_forward(hidden, ln)
+        two_step = hidden + m(ln(hidden))
+    m._op.query_status()
+    assert rel_err(out.cpu(), two_step.cpu()) < 2e-6
+
+
 def test_block_forward_argument_checks(cuda_device):
     m = PEER(64, 32, 256, num_experts_per_tok=4, num_heads=2, query_dim=32, product_key_dim=[16, 16]).to(cuda_device).eval()
     ln = torch.nn.LayerNorm(64).to(cuda_device)
