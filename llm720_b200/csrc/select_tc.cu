@@ -37,7 +37,11 @@
 // reprocesses (select_simt.cu), so the result never depends on the heuristic.
 //
 // Warps: 0 = TMA producer, 1 = MMA issuer, 2-3 idle, 4-19 = 16 scan warps
-// (scan warp s reads TMEM lanes 32*(s&3).. and columns 32*(s>>2)..).
+// (scan warp s reads TMEM lanes 32*(s&3).. and columns 32*(s>>2)..).  The four
+// warps with the same s>>2 produce and consume everything that belongs to
+// their 32 rows (group maxima, bounds, candidate lists, pool), so they
+// synchronise among themselves only (one named barrier per group) and the four
+// groups drift apart by up to the four accumulators in flight.
 // Ordering among exactly equal scores: smaller sub-key index first (per half),
 // smaller candidate position first (final), as in select_simt.cu.
 #include <float.h>
@@ -62,7 +66,7 @@ constexpr int MAX_GROUPS = 32;     // key groups per row and half whose maxima b
 constexpr int CAP = 32;            // candidates per row and half
 constexpr int LK = 16;             // list length per half (top_k and k' <= 16)
 constexpr int SCAN_WARPS = 16;
-constexpr int POOL = 256;          // candidates beyond CAP, all rows of the tile together
+constexpr int POOL = 64;           // candidates beyond CAP, per group of 32 rows (4 such pools per tile)
 constexpr int LOST = 1 << 20;      // added to a row's count when one of its candidates could not be kept
 constexpr int STAGE_CAP = 8;       // scores a lane can hold back per chunk before they go to the row lists
 constexpr int THREADS = 128 + SCAN_WARPS * 32;
@@ -79,8 +83,8 @@ struct Smem {
     static constexpr size_t tau_off = cnt_off + BM * 4;                                          // [128] int
     static constexpr size_t stage_off = gmax_off;          // [STAGE_CAP][512] float: pass 1 only, when the group maxima are dead
     static constexpr size_t pool_off = tau_off + BM * 4;                                         // [POOL] (row, score, sub-key, -)
-    static constexpr size_t bar_off = pool_off + POOL * 16;
-    static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 16 + 1008;
+    static constexpr size_t bar_off = pool_off + 4 * POOL * 16;
+    static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 32 + 1008;
 };
 static_assert(Smem::total <= 227 * 1024, "shared memory budget");
 static_assert(STAGE_CAP * SCAN_WARPS * 32 * 4 <= MAX_GROUPS * BM * 4, "the staging slots reuse the group maxima");
@@ -284,8 +288,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                         if (pos < CAP) {
                                             s_cand[row * CAP + pos] = make_int2(__float_as_int(x), key);
                                         } else {                             // a long list continues in the tile's pool
-                                            const int pp = atomicAdd(s_pool_cnt, 1);
-                                            if (pp < POOL) s_pool[pp] = make_int4(row, __float_as_int(x), key, 0);
+                                            const int pp = atomicAdd(s_pool_cnt + cg, 1);
+                                            if (pp < POOL) s_pool[cg * POOL + pp] = make_int4(row, __float_as_int(x), key, 0);
                                             else atomicAdd(&s_cnt[row], LOST);
                                         }
                                     } else {
@@ -305,7 +309,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             if ((lane & 3) == 0) s_gmax[(quarter * 8 + (lane >> 2)) * BM + cg * 32 + j] = m;
                         }
                     }
-                    asm volatile("bar.sync 1, 512;" ::: "memory");
+                    asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
                     if (pass == 0) {
                         // bound of my 8 rows: the 16th largest of the row's 32 group maxima (16 distinct scores reach it)
                         // (the 8 rows' sorting networks are written side by side so their shuffles overlap)
@@ -328,8 +332,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             const float t = __shfl_sync(FULL_MASK, tv[rr], LK - 1);
                             if (lane == 0) { s_tau[s * 8 + rr] = t; s_cnt[s * 8 + rr] = 0; }
                         }
-                        if (s == 0 && lane == 0) *s_pool_cnt = 0;
-                        asm volatile("bar.sync 1, 512;" ::: "memory");
+                        if ((s & 3) == 0 && lane == 0) s_pool_cnt[cg] = 0;
+                        asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
                     }
                 }
                 // the 16 best candidates of my 8 rows, in order (score descending, sub-key ascending)
@@ -362,12 +366,12 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             }
                         }
                     if (pooled) {                            // rare: insert the pool's entries of these rows
-                        const int np = min(*s_pool_cnt, POOL);
+                        const int np = min(s_pool_cnt[cg], POOL);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             if (!(pooled & (1u << q))) continue;
                             for (int e = 0; e < np; ++e) {
-                                const int4 pe = s_pool[e];
+                                const int4 pe = s_pool[cg * POOL + e];
                                 if (pe.x != s * 8 + rb + q) continue;
                                 const float ex = __int_as_float(pe.y);
                                 const bool before = (v[q] > ex) || (v[q] == ex && c[q] < pe.z);
