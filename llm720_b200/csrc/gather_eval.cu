@@ -131,6 +131,22 @@ __device__ __forceinline__ void dot4_e4m3_f16(uint32_t w, uint32_t x01, uint32_t
         : "+f"(d0), "+f"(d1)
         : "r"(w), "r"(x01), "r"(x23));
 }
+// sum of the 8 products of two 16-byte chunks of bf16 values (a bf16 x bf16 product is exact in fp32)
+__device__ __forceinline__ void dot8_bf16(const uint4& a, const uint32_t* b, float& d0, float& d1) {
+    asm("{\n\t"
+        ".reg .b16 a0, a1, b0, b1;\n\t"
+        "mov.b32 {a0, a1}, %2;\n\tmov.b32 {b0, b1}, %6;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %1, a1, b1, %1;\n\t"
+        "mov.b32 {a0, a1}, %3;\n\tmov.b32 {b0, b1}, %7;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %1, a1, b1, %1;\n\t"
+        "mov.b32 {a0, a1}, %4;\n\tmov.b32 {b0, b1}, %8;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %1, a1, b1, %1;\n\t"
+        "mov.b32 {a0, a1}, %5;\n\tmov.b32 {b0, b1}, %9;\n\t"
+        "fma.rn.f32.bf16 %0, a0, b0, %0;\n\tfma.rn.f32.bf16 %1, a1, b1, %1;\n\t"
+        "}"
+        : "+f"(d0), "+f"(d1)
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]));
+}
 __device__ __forceinline__ uint32_t pack_f16(float a, float b) {
     const __half2 v = __floats2half2_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&v);
@@ -201,7 +217,10 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
         }
         // The activation row stays in registers for the whole token: fp32, or (rows longer than 64
         // elements per lane, bf16 activations) as packed bf16 pairs widened at each use.
-        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH>::MANY && sizeof(XT) == 2);
+        // bf16 tables with bf16 activations: the activations stay packed and the down-row dot product runs on
+        // mixed-precision FMAs (no widening of either operand)
+        constexpr bool BFDOT = sizeof(TT) == 2 && sizeof(XT) == 2;
+        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH>::MANY && sizeof(XT) == 2) || BFDOT;
         // FP8 rows: the activations are kept as f16 pairs, scaled by a power of two so
         // that the row's largest magnitude lies in [1, 2) (a bf16 value then converts exactly unless it is more
         // than 2^14 times smaller than the largest), and the down-row dot product runs on mixed-precision FMAs.
@@ -288,6 +307,8 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
                             dot4_e4m3_f16(raw.y, xw[2], xw[3], d0, d1);
                             dot4_e4m3_f16(raw.z, xw[4], xw[5], d0, d1);
                             dot4_e4m3_f16(raw.w, xw[6], xw[7], d0, d1);
+                        } else if constexpr (BFDOT) {
+                            dot8_bf16(raw, xp + i * EPC / 2, d0, d1);
                         } else {
                             float f[EPC];
                             Chunk<TT>::decode(raw, f);
