@@ -28,15 +28,19 @@ constexpr int MAX_SMEM = 227 * 1024;
 // Warps per CTA (one CTA per SM) and ring bytes per warp.  Rows of a 16-bit or 32-bit table keep the memory
 // system busy with 8 warps; FP8 rows carry half the bytes per decoded element, so that instance is bound by
 // instruction issue and runs 14 warps with smaller rings and packed f16 activations (127 registers).
-template <typename TT, int CH> struct WarpCfg {
-    static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 12 warps
-    static constexpr int WARPS = MANY ? 14 : 8;
-    static constexpr int RING_BYTES = MANY ? 12 * 1024 : 24 * 1024;
+// W10 (bf16 rows of 4 KB only): ten warps on 20 KB rings, for layers whose selected rows stay L2-resident (the
+// reference's id arithmetic addresses at most n0 + n1 - 1 rows): there the stage is bound by instruction issue, not
+// by memory, and more warps help; with rows streaming from HBM eight warps on deeper rings are faster.
+template <typename TT, int CH, bool W10> struct WarpCfg {
+    static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 14 warps
+    static constexpr bool TEN = W10 && sizeof(TT) == 2 && CH == 8;
+    static constexpr int WARPS = MANY ? 14 : (TEN ? 10 : 8);
+    static constexpr int RING_BYTES = MANY ? 12 * 1024 : (TEN ? 20 * 1024 : 24 * 1024);
 };
 
-template <typename TT, int CH> struct RingCfg {
+template <typename TT, int CH, bool W10> struct RingCfg {
     static constexpr int SLOT = CH * 512;   // bytes: one row of up to CH 16-byte chunks per lane
-    static constexpr int ST0 = WarpCfg<TT, CH>::RING_BYTES / SLOT;
+    static constexpr int ST0 = WarpCfg<TT, CH, W10>::RING_BYTES / SLOT;
     static constexpr int STAGES = ST0 > MAX_STAGES ? MAX_STAGES : (ST0 < 2 ? 2 : ST0);
 };
 
@@ -162,10 +166,10 @@ struct GatherParams {
     const void* residual;      // optional [T, Dout] in the activation dtype, added to the result
 };
 
-template <typename XT, typename TT, int CH>
-__global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_kernel(const GatherParams p) {
-    using RC = RingCfg<TT, CH>;
-    constexpr int WARPS = WarpCfg<TT, CH>::WARPS;
+template <typename XT, typename TT, int CH, bool W10>
+__global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_eval_kernel(const GatherParams p) {
+    using RC = RingCfg<TT, CH, W10>;
+    constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
     constexpr int STAGES = RC::STAGES;
     constexpr int SLOT = RC::SLOT;
     constexpr int EPC = Chunk<TT>::N;            // elements per 16-byte chunk
@@ -220,7 +224,7 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
         // bf16 tables with bf16 activations: the activations stay packed and the down-row dot product runs on
         // mixed-precision FMAs (no widening of either operand)
         constexpr bool BFDOT = sizeof(TT) == 2 && sizeof(XT) == 2;
-        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH>::MANY && sizeof(XT) == 2) || BFDOT;
+        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH, W10>::MANY && sizeof(XT) == 2) || BFDOT;
         // FP8 rows: the activations are kept as f16 pairs, scaled by a power of two so
         // that the row's largest magnitude lies in [1, 2) (a bf16 value then converts exactly unless it is more
         // than 2^14 times smaller than the largest), and the down-row dot product runs on mixed-precision FMAs.
@@ -380,33 +384,41 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH>::WARPS * 32, 1) gather_eval_ke
     }
 }
 
-template <typename XT, typename TT, int CH>
+template <typename XT, typename TT, int CH, bool W10>
 size_t smem_bytes(int HK) {
-    using RC = RingCfg<TT, CH>;
-    constexpr int WARPS = WarpCfg<TT, CH>::WARPS;
+    using RC = RingCfg<TT, CH, W10>;
+    constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
     return static_cast<size_t>(WARPS) * RC::STAGES * RC::SLOT + WARPS * RC::STAGES * 8 +
            static_cast<size_t>(WARPS) * HK * (sizeof(TT) == 1 ? 16 : 8);
 }
 
-template <typename XT, typename TT, int CH>
-cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
-    const size_t smem = smem_bytes<XT, TT, CH>(a.HK);
+template <typename XT, typename TT, int CH, bool W10>
+cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
+    const size_t smem = smem_bytes<XT, TT, CH, W10>(a.HK);
     if (smem > MAX_SMEM) return cudaErrorInvalidValue;
     static bool configured[64] = {};    // per instantiation and device; the attribute is sticky per function
     int dev = 0;
     cudaError_t de = cudaGetDevice(&dev);
     if (de != cudaSuccess) return de;
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH>,
+        cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH, W10>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    constexpr int WARPS = WarpCfg<TT, CH>::WARPS;
+    constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
     int64_t ctas = (a.T + WARPS - 1) / WARPS;
     if (ctas > a.sm_count) ctas = a.sm_count;
-    gather_eval_kernel<XT, TT, CH><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(p);
+    gather_eval_kernel<XT, TT, CH, W10><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(p);
     return cudaGetLastError();
+}
+
+template <typename XT, typename TT, int CH>
+cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
+    if constexpr (sizeof(TT) == 2 && CH == 8) {
+        if (a.rows_l2_resident) return launch_w<XT, TT, CH, true>(a, p, s);
+    }
+    return launch_w<XT, TT, CH, false>(a, p, s);
 }
 
 template <typename XT, typename TT>

@@ -108,6 +108,7 @@ struct GatherArgs {
     int sm_count;
     int hidden;               // neurons per expert (rows are [hidden, D] / [Dout, hidden] blocks); 0 or 1 = single
     const void* residual;     // optional [T, Dout] act dtype: added to the result (out = residual + y)
+    int rows_l2_resident;     // hint: the ids address so few rows that they stay in L2 (reference id arithmetic)
     const int32_t* counts;    // optional [T]: how many of token t's HK entries are in use
     float* out_f32;           // optional fp32 output [T, Dout] (partial sums of a row-sharded table)
 };

@@ -421,6 +421,9 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
     g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.residual = residual;
+    // ids of the reference's arithmetic stay below n0 + n1: a few thousand rows, which live in L2
+    g.rows_l2_resident = c.index_mode == PEER_INDEX_REFERENCE && h->nd == 2 &&
+                         static_cast<int64_t>(c.n_keys0 + c.n_keys1) * (c.input_dim + c.output_dim) * act_bytes(c.table_dtype) <= (64LL << 20);
     const bool general_rows = h->hidden > 1 || c.act_dtype == PEER_DTYPE_F16;     // fp16 layers: the general kernel
     if (general_rows && g.hidden < 1) g.hidden = 1;
     cudaError_t e = general_rows ? launch_gather_hidden(g, s) : launch_gather_eval(g, s);
