@@ -154,9 +154,20 @@ int peer_project_queries(peer_handle_t h, const peer_tensors_t* t, int64_t n_tok
  * (experts.py:138-285).  queries fp32 [T, num_heads, query_dim] (after
  * LayerNorm, before the per-half L2 normalisation, exactly what the
  * reference function receives).  Writes ids int64 and raw scores fp32,
- * both [T, num_heads, top_k], sorted by descending score. */
+ * both [T, num_heads, top_k], sorted by descending score.  Runs the kernels peer_forward runs for
+ * this handle: the tensor-core selection on bf16 layers whose shape it covers (the given queries are
+ * normalised and split into bf16 terms first), the CUDA-core selection otherwise. */
 int peer_select(peer_handle_t h, const float* queries, const void* keys0, const void* keys1,
                 int64_t n_tokens, int64_t* ids_out, float* scores_out, void* stream);
+
+/* Counters of the tensor-core selection kernel's rare paths, accumulated since the last read (the
+ * read clears them; synchronises `stream`): *pooled_lists = (row, query half) pairs whose candidate
+ * list outgrew its 32 slots and continued in the shared pool; *refined_rows = rows that lost a
+ * candidate there and were redone by the exact CUDA-core kernel.  Both stay 0 on layers that run the
+ * CUDA-core selection.  The results never depend on these paths (each is exact); the counters let a
+ * test prove that a given input really exercised them.  The reference has one selection routine
+ * (PEER._get_expert_indices_pytorch, experts.py:138-285) and nothing to count. */
+int peer_select_stats(peer_handle_t h, int64_t* pooled_lists, int64_t* refined_rows, void* stream);
 
 /* Same retrieval for a key grid of any dimensionality (1 to 4; experts.py:195-270: the dimensions
  * are folded in one at a time and all but the last fold keep the best 4*top_k sums).  `keys` is an
@@ -182,6 +193,31 @@ int peer_gather_eval_partial(peer_handle_t h, const void* x, const int32_t* ids,
                              const int32_t* counts, int32_t entries_per_token, const void* expert_down,
                              const void* expert_up, const float* down_scale, const float* up_scale,
                              int64_t n_local_rows, float* out_f32, int64_t n_tokens, void* stream);
+
+/* The other per-rank pieces of the expert-parallel layer (no counterpart in the reference, see above).
+ *
+ * peer_select_tokens: query projection + selection only (experts.py:302-327): flat expert ids int32
+ * and softmax weights fp32, both [T, num_heads*top_k], into caller buffers - what this rank sends.
+ * t->expert_down / expert_up / out are not read; t->ids_out / scores_out are filled when given.
+ *
+ * peer_route_tuples (sender): buckets the T*entries_per_token tuples by owner = id / rows_per_rank into
+ * `send`, int32 [world, bucket_cap, 3] of (token_offset + token, id - owner*rows_per_rank, weight bits);
+ * a bucket keeps (token, slot) order and is padded with token -1; ids outside [0, world*rows_per_rank)
+ * are dropped.  bucket_cap >= T*entries_per_token always suffices.  world <= 64.
+ *
+ * peer_pack_tuples (receiver): `recv`, int32 [world, bucket_cap, 3] as it arrives from the all-to-all,
+ * becomes per-token lists ids_out int32 / weights_out fp32 [n_tokens, list_cap] and counts_out int32
+ * [n_tokens] (entries beyond list_cap are dropped, unused slots are zero), in (source rank, position)
+ * order: the input of peer_gather_eval_partial.
+ *
+ * Both routing kernels are deterministic (no atomics decide an order).  No handle; asynchronous. */
+int peer_select_tokens(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, int32_t* ids_out,
+                       float* weights_out, void* stream);
+int peer_route_tuples(const int32_t* ids, const float* weights, int64_t n_tokens, int32_t entries_per_token,
+                      int32_t token_offset, int64_t rows_per_rank, int32_t world, int64_t bucket_cap,
+                      int32_t* send, void* stream);
+int peer_pack_tuples(const int32_t* recv, int32_t world, int64_t bucket_cap, int64_t n_tokens, int32_t list_cap,
+                     int32_t* ids_out, float* weights_out, int32_t* counts_out, void* stream);
 
 /* Backward of peer_gather_eval: the gradients autograd derives for the expert evaluation of the
  * reference (llm/models/experts.py:332-382; exercised by tests/test_peer_integration.py:181-192 and
@@ -219,8 +255,10 @@ int peer_select_backward(peer_handle_t h, const float* queries, const void* cons
  * in it; larger calls return PEER_ERR_UNSUPPORTED with both sizes in peer_last_error(NULL).
  * Of `cfg` only abi_version, num_heads, query_dim, n_keys0, n_keys1, top_k, norm_keys, norm_query,
  * act_dtype (dtype of the sub-keys) and index_mode are read.  The first call on each device does
- * a one-time set-up (address of the array, kernel attribute): make it at start-up, before any
- * stream capture.  All calls share the array: calls whose kernels may overlap on the GPU race. */
+ * a one-time set-up (address of the array, kernel attribute; serialised by a lock): make it at
+ * start-up, before any stream capture.  Every later call only enqueues kernels on `stream`: it
+ * reads no host memory and does not synchronise.  All calls share the array: calls whose kernels
+ * may overlap on the GPU race. */
 int peer_select_noalloc(const peer_config_t* cfg, const float* queries, const void* keys0,
                         const void* keys1, int64_t n_tokens, int64_t* ids_out, float* scores_out,
                         void* stream);

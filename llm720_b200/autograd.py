@@ -19,7 +19,11 @@ dropout (training mode) the stages are separate nodes:
   per-slot factor, folded into the weights because each expert has one neuron);
 * expert evaluation: ``peer_gather_eval`` forward, ``peer_gather_eval_backward``
   backward (``_ExpertEval``): dense table gradients accumulated with vector
-  reductions, in the parameters' own dtype for single-neuron experts.
+  reductions in fp32 and rounded once to the parameters' dtype, which is what
+  the reference's embedding backward does for a bf16 layer (each row's sum is
+  formed in fp32).  ``module.table_grad_sums = "table"`` opts a bf16 layer into
+  sums formed in bf16 (half the traffic, one rounding per addend: only safe when
+  few tokens share a row).
 """
 from __future__ import annotations
 
@@ -53,29 +57,31 @@ class _ProjectQueries(torch.autograd.Function):
 
 class _ExpertEval(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weights, ids32, down, up, op):
+    def forward(ctx, x, weights, ids32, down, up, op, direct=False):
         ctx.save_for_backward(x, weights, ids32, down, up)
         ctx.op = op
+        ctx.direct = direct
         return op.gather_eval(x, ids32, weights.contiguous(), down, up)
 
     @staticmethod
     def backward(ctx, grad_out):
         x, weights, ids32, down, up = ctx.saved_tensors
-        # single-neuron experts of a bf16 layer: the table gradients are summed in bf16, in the buffers that become
-        # the parameters' .grad (the reference's bf16 training sums them in bf16 too); otherwise fp32, then cast
-        direct = (ctx.op.cfg.expert_hidden_size == 1 and down.dtype != torch.float16 and
-                  max(down.shape[1], up.shape[1]) * down.element_size() <= 4096)
+        direct = ctx.direct
         gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up,
                                                      grad_dtype=down.dtype if direct else torch.float32)
         need = ctx.needs_input_grad
         return (gx.to(x.dtype) if need[0] else None, gw if need[1] else None, None,
-                gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None)
+                gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None, None)
 
 
 def _sums_in_table_dtype(module, table) -> bool:
-    """Single-neuron experts with rows of at most 4 KB: the gradient kernel sums straight into a table of the
-    parameters' dtype.  Otherwise fp32 sums and a cast."""
-    return (module.expert_hidden_size == 1 and table.dtype != torch.float16 and
+    """Whether the gradient kernel sums straight into a table of the parameters' 16-bit dtype.  Off unless the
+    module asks for it (``table_grad_sums = "table"``): a bf16 running sum loses small addends once a row
+    collects many contributions (with the reference's id arithmetic, ids < n0 + n1, a row of the 1 M-expert
+    layer takes about a thousand per batch).  Only single-neuron experts with rows of at most 4 KB have that
+    kernel form."""
+    return (getattr(module, "table_grad_sums", "fp32") == "table" and module.expert_hidden_size == 1 and
+            table.dtype == torch.bfloat16 and
             max(module.input_dim, module.output_dim) * table.element_size() <= 4096)
 
 
@@ -207,7 +213,8 @@ def _forward_with_dropout(module, x, w, B, S):
     weights = torch.softmax(scores, dim=-1)
     weights = weights * F.dropout(torch.ones_like(weights), module.dropout.p, True)
     out = _ExpertEval.apply(x, weights.view(T, H * k), flat.to(torch.int32).view(T, H * k),
-                            module.expert_down.weight, module.expert_up.weight, op)
+                            module.expert_down.weight, module.expert_up.weight, op,
+                            _sums_in_table_dtype(module, module.expert_down.weight))
     if module.track_indices:
         module._stash(flat, scores.detach(), B, S)
     return out.view(B, S, module.output_dim)

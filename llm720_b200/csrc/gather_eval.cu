@@ -15,6 +15,8 @@
 // enough bytes in flight (about 190 KB per SM) to cover HBM latency.
 // Every wait is bounded; a wait that runs out records STATUS_TIMEOUT and the
 // warp stops, it never spins forever.
+#include <atomic>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -396,15 +398,17 @@ template <typename XT, typename TT, int CH, bool W10>
 cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
     const size_t smem = smem_bytes<XT, TT, CH, W10>(a.HK);
     if (smem > MAX_SMEM) return cudaErrorInvalidValue;
-    static bool configured[64] = {};    // per instantiation and device; the attribute is sticky per function
+    // Per instantiation and device; the attribute is sticky per function.  Setting it twice is harmless, so
+    // two host threads (two handles) that meet here need only see a consistent flag: an atomic, no lock.
+    static std::atomic<bool> configured[64];
     int dev = 0;
     cudaError_t de = cudaGetDevice(&dev);
     if (de != cudaSuccess) return de;
-    if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
         cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH, W10>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
         if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) configured[dev] = true;
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
     constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
     int64_t ctas = (a.T + WARPS - 1) / WARPS;
@@ -437,8 +441,6 @@ cudaError_t launch_ch(const GatherArgs& a, const GatherParams& p, int max_ch, cu
 }
 
 }  // namespace
-
-cudaError_t gather_eval_setup() { return cudaSuccess; }
 
 cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
     if (a.T == 0) return cudaSuccess;

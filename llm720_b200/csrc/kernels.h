@@ -50,6 +50,8 @@ struct SelectTcArgs {
     int sm_count;
     int32_t* overflow_rows;        // [rows]: rows the kernel leaves to the exact kernel (clustered scores)
     int* overflow_count;           // device counter, zeroed by the caller before the launch
+    unsigned long long* stats;     // optional [2], accumulated: row-halves whose candidate list continued in the
+                                   // pool; rows handed to the exact kernel
 };
 bool select_tc_supported(int act_dtype, int Q, int n0, int n1, int k, int kp0, int kp1);
 cudaError_t select_tc_setup();
@@ -61,9 +63,10 @@ cudaError_t launch_key_inv_norms(const void* keys, int n, int width, int do_norm
 // written [rows, width], or [width, rows] when transpose_out
 cudaError_t launch_normalize_rows(const void* in, int in_dtype, int64_t rows, int width, int do_norm,
                                   int transpose_out, float* out, cudaStream_t s);
-// [rows, Q] fp32 -> both halves of every row L2-normalised
+// [rows, Q] fp32 -> both halves of every row L2-normalised, as fp32 (`out`, optional) and/or as the three
+// bf16 terms hi/mid/lo the tensor-core select kernel takes (`split`, optional; arrays split_stride apart)
 cudaError_t launch_normalize_halves(const float* q, int64_t rows, int Q, int do_norm, float* out,
-                                    cudaStream_t s);
+                                    cudaStream_t s, __nv_bfloat16* split = nullptr, int64_t split_stride = 0);
 
 struct SelectArgs {
     const float* q_hat;   // [rows, Q] fp32, halves normalised
@@ -175,14 +178,22 @@ struct SelectGradArgs {
     const float* scores;        // [rows, k] raw scores of the forward pass
     const float* grad_weights;  // [rows, k] dL/d softmax weights
     float* grad_q;              // [rows, Q] written
+    int* status;                // device status word: STATUS_BOUNDS when a grid position lies outside the key grid
 };
 cudaError_t launch_select_grad(const SelectGradArgs& a, cudaStream_t s);
+
+// Tuple routing of the expert-parallel layer (route.cu).  send: [world, bucket_cap, 3] int32 buckets of
+// (global token | -1, local row, weight bits); recv: the same shape as received from the peers.
+cudaError_t launch_route_tuples(const int32_t* ids, const float* weights, int64_t n_tokens, int entries_per_token,
+                                int token_offset, int64_t rows_per_rank, int world, int64_t bucket_cap, int32_t* send,
+                                cudaStream_t s);
+cudaError_t launch_pack_tuples(const int32_t* recv, int world, int64_t bucket_cap, int64_t n_tokens, int list_cap,
+                               int32_t* ids_out, float* weights_out, int32_t* counts_out, cudaStream_t s);
 
 // LayerNorm over the model dimension, fp32 parameters (block_ln.cu)
 cudaError_t launch_block_ln(const void* x, int act_dtype, int64_t rows, int D, const float* w, const float* b, float eps,
                             void* out, cudaStream_t s);
 // one-time per-process attribute set-up (dynamic shared memory opt-in)
-cudaError_t gather_eval_setup();
 cudaError_t select_simt_setup();
 
 }  // namespace peer

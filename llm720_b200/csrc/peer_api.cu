@@ -38,6 +38,7 @@ struct peer_op {
     float* invn1 = nullptr;       // [n1]
     int32_t* ovf_rows = nullptr;  // [max_tokens*H] rows the tensor-core select leaves to the exact kernel
     int* ovf_count = nullptr;
+    unsigned long long* sel_stats = nullptr;   // [2] accumulated: pooled row-halves, rows redone by the exact kernel
     void* x_ln = nullptr;         // [max_tokens, D] act dtype: LayerNorm of the block input (peer_block_forward)
     int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
     float* sel_w = nullptr;       // [max_tokens, H*k]
@@ -102,7 +103,7 @@ static int candidates_per_dim(int top_k, int dim_size, int num_dims = 2) {
 namespace peer { int candidates_per_dim_2d(int top_k, int dim_size) { return candidates_per_dim(top_k, dim_size); } }
 
 static void free_all(peer_op* h) {
-    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->ovf_rows); cudaFree(h->ovf_count); cudaFree(h->sel_ids);
+    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->ovf_rows); cudaFree(h->ovf_count); cudaFree(h->sel_stats); cudaFree(h->sel_ids);
     cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status); cudaFree(h->x_ln);
     for (int b = 0; b < 2; ++b) {
         cudaFree(h->d_x[b]); cudaFree(h->d_out[b]); cudaFree(h->d_ids[b]); cudaFree(h->d_sc[b]);
@@ -218,7 +219,6 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
         if (eg == cudaSuccess) eg = cudaMalloc(reinterpret_cast<void**>(&h->sel_w), sizeof(float) * c->max_tokens * HKg);
         if (eg == cudaSuccess) eg = cudaMalloc(reinterpret_cast<void**>(&h->status), sizeof(int));
         if (eg == cudaSuccess) eg = cudaMemset(h->status, 0, sizeof(int));
-        if (eg == cudaSuccess) eg = gather_eval_setup();
         if (eg != cudaSuccess) {
             fail(nullptr, PEER_ERR_CUDA, "peer_create: %s", cudaGetErrorString(eg));
             free_all(h);
@@ -267,6 +267,8 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
         alloc(reinterpret_cast<void**>(&h->invn1), sizeof(float) * c->n_keys1);
         alloc(reinterpret_cast<void**>(&h->ovf_rows), sizeof(int32_t) * c->max_tokens * c->num_heads);
         alloc(reinterpret_cast<void**>(&h->ovf_count), sizeof(int));
+        alloc(reinterpret_cast<void**>(&h->sel_stats), 2 * sizeof(unsigned long long));
+        if (e == cudaSuccess) e = cudaMemset(h->sel_stats, 0, 2 * sizeof(unsigned long long));
     }
     if (h->use_tc)
         alloc(reinterpret_cast<void**>(&h->q_split), sizeof(__nv_bfloat16) * 3 * c->max_tokens * c->num_heads * c->query_dim);
@@ -277,7 +279,6 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
     if (e == cudaSuccess) e = cudaMemcpy(h->pairs, pairs.data(), sizeof(uint16_t) * pairs.size(), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(h->status, 0, sizeof(int));
     if (e == cudaSuccess) e = select_simt_setup();
-    if (e == cudaSuccess) e = gather_eval_setup();
     if (e == cudaSuccess && h->use_tc) e = query_tc_setup();
     if (e == cudaSuccess && h->use_tc_select) e = select_tc_setup();
     if (e != cudaSuccess) {
@@ -345,6 +346,30 @@ static SelectArgs select_args(peer_op* h, int64_t n_tokens) {
     return a;
 }
 
+// Tensor-core selection of one slice from h->q_split (hi/mid/lo terms of the normalised queries), followed by
+// the exact CUDA-core kernel on the rows the tensor-core kernel handed over (none for ordinary data).
+static int select_tc_slice(peer_op* h, const void* keys0, const void* keys1, int64_t n, int32_t* ids32, float* weights,
+                           int64_t* ids_out, float* scores_out, int32_t* prod_out, cudaStream_t s) {
+    const peer_config_t& c = h->cfg;
+    SelectTcArgs ta{};
+    ta.q_split = h->q_split; ta.term_rows = c.max_tokens * c.num_heads; ta.keys0 = keys0; ta.keys1 = keys1;
+    ta.invn0 = h->invn0; ta.invn1 = h->invn1; ta.rows = n * c.num_heads; ta.Q = c.query_dim;
+    ta.n0 = c.n_keys0; ta.n1 = c.n_keys1; ta.kp0 = h->kp0; ta.kp1 = h->kp1; ta.k = h->k_final;
+    ta.mult0 = h->mult0; ta.mult1 = h->mult1; ta.ids32 = ids32; ta.weights = weights;
+    ta.ids64 = ids_out; ta.raw_scores = scores_out; ta.status = h->status; ta.sm_count = h->sm_count;
+    ta.prod_ids = prod_out;
+    ta.overflow_rows = h->ovf_rows; ta.overflow_count = h->ovf_count; ta.stats = h->sel_stats;
+    CU_TRY(h, cudaMemsetAsync(h->ovf_count, 0, sizeof(int), s));
+    CU_TRY(h, launch_select_tc(ta, s));
+    SelectArgs fx = select_args(h, n);
+    fx.q_hat = nullptr; fx.q_split = h->q_split; fx.split_stride = c.max_tokens * c.num_heads * c.query_dim;
+    fx.row_list = h->ovf_rows; fx.row_count = h->ovf_count;
+    fx.ids32 = ids32; fx.weights = weights; fx.ids64 = ids_out; fx.raw_scores = scores_out;
+    fx.prod_ids = prod_out;
+    CU_TRY(h, launch_select_simt(fx, s));
+    return PEER_OK;
+}
+
 // One slice (n <= max_tokens) of the layer, all pointers on the device.
 static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, void* out, int64_t* ids_out,
                          float* scores_out, int64_t n, cudaStream_t s, const void* residual = nullptr,
@@ -389,23 +414,8 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         if (se == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "selection over this key grid is not implemented");
         CU_TRY(h, se);
     } else if (h->use_tc_select) {
-        SelectTcArgs ta{};
-        ta.q_split = h->q_split; ta.term_rows = c.max_tokens * c.num_heads; ta.keys0 = t->keys0; ta.keys1 = t->keys1;
-        ta.invn0 = h->invn0; ta.invn1 = h->invn1; ta.rows = n * c.num_heads; ta.Q = c.query_dim;
-        ta.n0 = c.n_keys0; ta.n1 = c.n_keys1; ta.kp0 = h->kp0; ta.kp1 = h->kp1; ta.k = h->k_final;
-        ta.mult0 = h->mult0; ta.mult1 = h->mult1; ta.ids32 = h->sel_ids; ta.weights = h->sel_w;
-        ta.ids64 = ids_out; ta.raw_scores = scores_out; ta.status = h->status; ta.sm_count = h->sm_count;
-        ta.prod_ids = prod_out;
-        ta.overflow_rows = h->ovf_rows; ta.overflow_count = h->ovf_count;
-        CU_TRY(h, cudaMemsetAsync(h->ovf_count, 0, sizeof(int), s));
-        CU_TRY(h, launch_select_tc(ta, s));
-        // rows whose candidate lists overflowed (none for ordinary data) are redone exactly
-        SelectArgs fx = select_args(h, n);
-        fx.q_hat = nullptr; fx.q_split = h->q_split; fx.split_stride = c.max_tokens * c.num_heads * c.query_dim;
-        fx.row_list = h->ovf_rows; fx.row_count = h->ovf_count;
-        fx.ids32 = h->sel_ids; fx.weights = h->sel_w; fx.ids64 = ids_out; fx.raw_scores = scores_out;
-        fx.prod_ids = prod_out;
-        CU_TRY(h, launch_select_simt(fx, s));
+        const int rc_sel = select_tc_slice(h, t->keys0, t->keys1, n, h->sel_ids, h->sel_w, ids_out, scores_out, prod_out, s);
+        if (rc_sel) return rc_sel;
         h->launches += 1;
     } else {
         SelectArgs sa = select_args(h, n);
@@ -414,6 +424,11 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         CU_TRY(h, launch_select_simt(sa, s));
     }
     if (ev) CU_TRY(h, cudaEventRecord(ev[2], s));
+    if (!out) {                 // query and selection stages only (peer_select_tokens)
+        if (ev) CU_TRY(h, cudaEventRecord(ev[3], s));
+        h->launches += 2;
+        return PEER_OK;
+    }
 
     GatherArgs g{};
     g.x = x; g.ids = h->sel_ids; g.weights = h->sel_w; g.down = t->expert_down; g.up = t->expert_up;
@@ -657,11 +672,23 @@ extern "C" int peer_select(peer_handle_t h, const float* queries, const void* ke
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     int rc = normalise_keys(h, keys0, keys1, s);
+    if (!rc && h->use_tc_select) rc = key_inv_norms(h, keys0, keys1, s);
     if (rc) return rc;
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
     const int64_t HQ = static_cast<int64_t>(c.num_heads) * c.query_dim;
     for (int64_t t0 = 0; t0 < n_tokens; t0 += c.max_tokens) {
         const int64_t n = n_tokens - t0 < c.max_tokens ? n_tokens - t0 : c.max_tokens;
+        if (h->use_tc_select) {
+            // the same kernels the whole layer runs: the given fp32 queries are normalised and split into the
+            // three bf16 terms the tensor-core kernel contracts
+            CU_TRY(h, launch_normalize_halves(queries + t0 * HQ, n * c.num_heads, c.query_dim, c.norm_query, nullptr, s,
+                                              h->q_split, c.max_tokens * HQ));
+            rc = select_tc_slice(h, keys0, keys1, n, nullptr, nullptr, ids_out ? ids_out + t0 * HK : nullptr,
+                                 scores_out ? scores_out + t0 * HK : nullptr, nullptr, s);
+            if (rc) return rc;
+            h->launches += 3;
+            continue;
+        }
         CU_TRY(h, launch_normalize_halves(queries + t0 * HQ, n * c.num_heads, c.query_dim, c.norm_query, h->q_hat, s));
         SelectArgs sa = select_args(h, n);
         sa.ids64 = ids_out ? ids_out + t0 * HK : nullptr;
@@ -669,6 +696,80 @@ extern "C" int peer_select(peer_handle_t h, const float* queries, const void* ke
         CU_TRY(h, launch_select_simt(sa, s));
         h->launches += 2;
     }
+    return PEER_OK;
+}
+
+extern "C" int peer_select_tokens(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, int32_t* ids_out,
+                                  float* weights_out, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (n_tokens < 0) return fail(h, PEER_ERR_INVALID_ARG, "negative token count");
+    if (n_tokens == 0) return PEER_OK;
+    if (!ids_out || !weights_out) return fail(h, PEER_ERR_INVALID_ARG, "peer_select_tokens: ids_out and weights_out are required");
+    int rc = check_tensors(h, t, false);
+    if (rc) return rc;
+    const peer_config_t& c = h->cfg;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, s);
+    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
+    if (rc) return rc;
+    const int ab = act_bytes(c.act_dtype);
+    const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
+    for (int64_t t0 = 0; t0 < n_tokens; t0 += c.max_tokens) {
+        const int64_t n = n_tokens - t0 < c.max_tokens ? n_tokens - t0 : c.max_tokens;
+        rc = forward_slice(h, t, static_cast<const char*>(t->x) + t0 * c.input_dim * ab, nullptr,
+                           t->ids_out ? t->ids_out + t0 * HK : nullptr, t->scores_out ? t->scores_out + t0 * HK : nullptr,
+                           n, s);
+        if (rc) return rc;
+        CU_TRY(h, cudaMemcpyAsync(ids_out + t0 * HK, h->sel_ids, sizeof(int32_t) * n * HK, cudaMemcpyDeviceToDevice, s));
+        CU_TRY(h, cudaMemcpyAsync(weights_out + t0 * HK, h->sel_w, sizeof(float) * n * HK, cudaMemcpyDeviceToDevice, s));
+    }
+    return PEER_OK;
+}
+
+extern "C" int peer_route_tuples(const int32_t* ids, const float* weights, int64_t n_tokens, int32_t entries_per_token,
+                                 int32_t token_offset, int64_t rows_per_rank, int32_t world, int64_t bucket_cap,
+                                 int32_t* send, void* stream) {
+    if (!ids || !weights || !send || n_tokens < 0) {
+        peer::set_global_error("peer_route_tuples: null pointer or negative token count");
+        return PEER_ERR_INVALID_ARG;
+    }
+    const cudaError_t e = launch_route_tuples(ids, weights, n_tokens, entries_per_token, token_offset, rows_per_rank,
+                                              world, bucket_cap, send, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue) {
+        peer::set_global_error("peer_route_tuples: world must be 1..64, rows_per_rank, entries_per_token and bucket_cap positive");
+        return PEER_ERR_INVALID_ARG;
+    }
+    if (e != cudaSuccess) { peer::set_global_error(cudaGetErrorString(e)); return PEER_ERR_CUDA; }
+    return PEER_OK;
+}
+
+extern "C" int peer_pack_tuples(const int32_t* recv, int32_t world, int64_t bucket_cap, int64_t n_tokens, int32_t list_cap,
+                                int32_t* ids_out, float* weights_out, int32_t* counts_out, void* stream) {
+    if (!recv || !ids_out || !weights_out || !counts_out || n_tokens < 0) {
+        peer::set_global_error("peer_pack_tuples: null pointer or negative token count");
+        return PEER_ERR_INVALID_ARG;
+    }
+    const cudaError_t e = launch_pack_tuples(recv, world, bucket_cap, n_tokens, list_cap, ids_out, weights_out, counts_out,
+                                             static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue) {
+        peer::set_global_error("peer_pack_tuples: world, bucket_cap and list_cap must be positive");
+        return PEER_ERR_INVALID_ARG;
+    }
+    if (e != cudaSuccess) { peer::set_global_error(cudaGetErrorString(e)); return PEER_ERR_CUDA; }
+    return PEER_OK;
+}
+
+extern "C" int peer_select_stats(peer_handle_t h, int64_t* pooled_lists, int64_t* refined_rows, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    unsigned long long v[2] = {0, 0};
+    if (h->sel_stats) {
+        cudaStream_t s = static_cast<cudaStream_t>(stream);
+        CU_TRY(h, cudaMemcpyAsync(v, h->sel_stats, sizeof v, cudaMemcpyDeviceToHost, s));
+        CU_TRY(h, cudaMemsetAsync(h->sel_stats, 0, sizeof v, s));
+        CU_TRY(h, cudaStreamSynchronize(s));
+    }
+    if (pooled_lists) *pooled_lists = static_cast<int64_t>(v[0]);
+    if (refined_rows) *refined_rows = static_cast<int64_t>(v[1]);
     return PEER_OK;
 }
 
@@ -713,6 +814,7 @@ extern "C" int peer_select_backward(peer_handle_t h, const float* queries, const
     ga.nd = h->nd; ga.Q = c.query_dim; ga.k = c.top_k; ga.norm_keys = c.norm_keys; ga.norm_query = c.norm_query;
     ga.act_dtype = c.act_dtype; ga.rows = n_tokens * c.num_heads;
     ga.prod_ids = product_ids; ga.scores = scores; ga.grad_weights = grad_weights; ga.grad_q = grad_queries;
+    ga.status = h->status;
     cudaError_t e = launch_select_grad(ga, static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "score-path backward: this key grid is not implemented");
     CU_TRY(h, e);
@@ -828,6 +930,6 @@ extern "C" int peer_query_status(peer_handle_t h, void* stream) {
     CU_TRY(h, cudaMemsetAsync(h->status, 0, sizeof(int), s));
     CU_TRY(h, cudaStreamSynchronize(s));
     if (st == STATUS_TIMEOUT) return fail(h, PEER_ERR_DEVICE_TIMEOUT, "a bounded device-side wait ran out");
-    if (st == STATUS_BOUNDS) return fail(h, PEER_ERR_BOUNDS, "an expert id outside [0, num_experts) was skipped");
+    if (st == STATUS_BOUNDS) return fail(h, PEER_ERR_BOUNDS, "an expert id outside [0, num_experts) (or a grid position outside the key grid) was skipped");
     return PEER_OK;
 }

@@ -183,8 +183,12 @@ __global__ void normalize_rows_kernel(const T* __restrict__ in, int64_t rows, in
     }
 }
 
+// out (optional): the normalised values in fp32.  split (optional): the same values as three bf16 terms
+// (hi + mid + lo carry the 24 bits of the fp32 value), the three arrays split_stride elements apart: the
+// operand format of the tensor-core select kernel.
 __global__ void normalize_halves_kernel(const float* __restrict__ q, int64_t rows, int Q, int do_norm,
-                                        float* __restrict__ out) {
+                                        float* __restrict__ out, __nv_bfloat16* __restrict__ split,
+                                        int64_t split_stride) {
     const int lane = threadIdx.x & 31;
     const int64_t r = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
     if (r >= rows) return;
@@ -198,7 +202,16 @@ __global__ void normalize_halves_kernel(const float* __restrict__ q, int64_t row
     const float n1 = do_norm ? fmaxf(sqrtf(warp_sum(s1)), NORM_EPS) : 1.0f;
     for (int c = lane; c < Q; c += 32) {
         const float v = q[r * Q + c];
-        out[r * Q + c] = do_norm ? v / (c < half ? n0 : n1) : v;
+        const float y = do_norm ? v / (c < half ? n0 : n1) : v;
+        if (out) out[r * Q + c] = y;
+        if (split) {
+            float rem = y;
+            const __nv_bfloat16 hi = __float2bfloat16_rn(rem); rem -= __bfloat162float(hi);
+            const __nv_bfloat16 mid = __float2bfloat16_rn(rem); rem -= __bfloat162float(mid);
+            split[r * Q + c] = hi;
+            split[split_stride + r * Q + c] = mid;
+            split[2 * split_stride + r * Q + c] = __float2bfloat16_rn(rem);
+        }
     }
 }
 
@@ -247,10 +260,10 @@ cudaError_t launch_normalize_rows(const void* in, int in_dtype, int64_t rows, in
 }
 
 cudaError_t launch_normalize_halves(const float* q, int64_t rows, int Q, int do_norm, float* out,
-                                    cudaStream_t s) {
+                                    cudaStream_t s, __nv_bfloat16* split, int64_t split_stride) {
     if (rows == 0) return cudaSuccess;
     const unsigned blocks = static_cast<unsigned>((rows * 32 + 255) / 256);
-    normalize_halves_kernel<<<blocks, 256, 0, s>>>(q, rows, Q, do_norm, out);
+    normalize_halves_kernel<<<blocks, 256, 0, s>>>(q, rows, Q, do_norm, out, split, split_stride);
     return cudaGetLastError();
 }
 

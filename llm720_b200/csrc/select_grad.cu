@@ -23,6 +23,8 @@ template <typename T>
 __global__ void __launch_bounds__(WARPS * 32) select_grad_kernel(const SelectGradArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int width = a.Q / a.nd;
+    long long total = 1;
+    for (int d = 0; d < a.nd; ++d) total *= a.n[d];
     for (int64_t row = static_cast<int64_t>(blockIdx.x) * WARPS + warp; row < a.rows;
          row += static_cast<int64_t>(gridDim.x) * WARPS) {
         // softmax weights and ds, one selected expert per lane
@@ -34,8 +36,14 @@ __global__ void __launch_bounds__(WARPS * 32) select_grad_kernel(const SelectGra
         const float e = live ? expf(s - mx) : 0.f;
         const float w = e / warp_sum(e);
         const float dw = live ? a.grad_weights[row * a.k + lane] : 0.f;
-        const float ds = w * (dw - warp_sum(w * dw));
-        const int pid = live ? a.prod_ids[row * a.k + lane] : 0;
+        float ds = w * (dw - warp_sum(w * dw));
+        int pid = live ? a.prod_ids[row * a.k + lane] : 0;
+        // a grid position outside the key grid is recorded and contributes nothing; it is never used as an address
+        if (pid < 0 || pid >= total) {
+            if (a.status) atomicMax(a.status, STATUS_BOUNDS);
+            pid = 0;
+            ds = 0.f;
+        }
         for (int d = 0; d < a.nd; ++d) {
             const int my_idx = static_cast<int>((pid / a.stride[d]) % a.n[d]);
             const T* __restrict__ keys = static_cast<const T*>(a.keys[d]);

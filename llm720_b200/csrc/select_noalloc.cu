@@ -17,11 +17,13 @@
 //    overwrites what it reads), but two calls whose kernels overlap on the GPU (different
 //    streams, no dependency) race on it and produce garbage: serialise them;
 //  * the first call on each device looks up the array's device address and raises the
-//    shared-memory limit of the selection kernel; make that first call during start-up,
-//    outside any stream capture.
+//    shared-memory limit of the selection kernel (under a lock, so two host threads may make
+//    it at once); make that first call during start-up, outside any stream capture.  Every
+//    later call only enqueues kernels on the caller's stream: nothing is copied from host
+//    memory (the candidate-pair table is written by a kernel), and nothing synchronises.
 #include <cmath>
 #include <cstdio>
-#include <vector>
+#include <mutex>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -36,7 +38,18 @@ namespace peer { void set_global_error(const char* msg); int candidates_per_dim_
 
 namespace {
 constexpr int MAX_DEVICES = 64;
-unsigned char* g_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device
+unsigned char* g_scratch_ptr[MAX_DEVICES] = {};   // device address of the array, per device (guarded by g_setup_lock)
+std::mutex g_setup_lock;
+
+// Candidate pairs (a, b) with (a+1)(b+1) <= k, a-major: the only ones that can reach the final top k
+// because both per-half lists are sorted.  Written on the device so that a call never reads host memory.
+__global__ void noalloc_pairs_kernel(uint16_t* pairs, int kp0, int kp1, int k, int cap) {
+    if (threadIdx.x || blockIdx.x) return;
+    int n = 0;
+    for (int a = 0; a < kp0; ++a)
+        for (int b = 0; b < kp1; ++b)
+            if ((a + 1) * (b + 1) <= k && n < cap) pairs[n++] = static_cast<uint16_t>((a << 8) | b);
+}
 
 int refuse(int code, const char* fmt, long long a = 0, long long b = 0, long long c = 0) {
     char buf[384];
@@ -58,6 +71,8 @@ extern "C" int peer_select_noalloc(const peer_config_t* c, const float* queries,
     if (n_tokens == 0) return PEER_OK;
     if (c->act_dtype != PEER_DTYPE_F32 && c->act_dtype != PEER_DTYPE_BF16)
         return refuse(PEER_ERR_UNSUPPORTED, "peer_select_noalloc: sub-keys must be fp32 or bf16");
+    if (c->index_mode != PEER_INDEX_REFERENCE && c->index_mode != PEER_INDEX_PRODUCT)
+        return refuse(PEER_ERR_INVALID_ARG, "peer_select_noalloc: index_mode %lld", c->index_mode);
     if (c->query_dim <= 0 || c->query_dim % 2 || c->query_dim > 256 || c->num_heads <= 0 || c->n_keys0 <= 0 ||
         c->n_keys1 <= 0 || c->top_k <= 0 || c->top_k > 32)
         return refuse(PEER_ERR_UNSUPPORTED, "peer_select_noalloc: query_dim even and <= 256, top_k <= 32, positive sizes");
@@ -84,35 +99,37 @@ extern "C" int peer_select_noalloc(const peer_config_t* c, const float* queries,
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES)
         return refuse(PEER_ERR_CUDA, "peer_select_noalloc: cudaGetDevice failed or device index out of range");
-    if (!g_scratch_ptr[dev]) {
-        unsigned char* ptr = nullptr;
-        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
-        if (e != cudaSuccess || !ptr) {
-            peer::set_global_error(cudaGetErrorString(e));
-            return PEER_ERR_CUDA;
+    unsigned char* base = nullptr;
+    {
+        std::lock_guard<std::mutex> guard(g_setup_lock);
+        if (!g_scratch_ptr[dev]) {
+            unsigned char* ptr = nullptr;
+            e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_scratch);
+            if (e != cudaSuccess || !ptr) {
+                peer::set_global_error(cudaGetErrorString(e));
+                return PEER_ERR_CUDA;
+            }
+            e = select_simt_setup();
+            if (e != cudaSuccess) { peer::set_global_error(cudaGetErrorString(e)); return PEER_ERR_CUDA; }
+            g_scratch_ptr[dev] = ptr;
         }
-        e = select_simt_setup();
-        if (e != cudaSuccess) { peer::set_global_error(cudaGetErrorString(e)); return PEER_ERR_CUDA; }
-        g_scratch_ptr[dev] = ptr;
+        base = g_scratch_ptr[dev];
     }
-    unsigned char* base = g_scratch_ptr[dev];
     float* khat0 = reinterpret_cast<float*>(base);
     float* khat1 = reinterpret_cast<float*>(base + k0_bytes);
     float* q_hat = reinterpret_cast<float*>(base + k0_bytes + k1_bytes);
     uint16_t* pairs_dev = reinterpret_cast<uint16_t*>(base + k0_bytes + k1_bytes + q_bytes);
 
-    // candidate pairs (a, b) with (a+1)(b+1) <= k: the only ones that can reach the final top k
-    uint16_t pairs[MAX_PAIRS];
+    // how many candidate pairs the device-side enumeration will write
     int n_pairs = 0;
     for (int a = 0; a < kp0; ++a)
         for (int b = 0; b < kp1; ++b)
-            if ((a + 1) * (b + 1) <= c->top_k) {
-                if (n_pairs == MAX_PAIRS) return refuse(PEER_ERR_UNSUPPORTED, "peer_select_noalloc: too many candidate pairs");
-                pairs[n_pairs++] = static_cast<uint16_t>((a << 8) | b);
-            }
+            if ((a + 1) * (b + 1) <= c->top_k) ++n_pairs;
+    if (n_pairs > MAX_PAIRS) return refuse(PEER_ERR_UNSUPPORTED, "peer_select_noalloc: too many candidate pairs");
 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    e = cudaMemcpyAsync(pairs_dev, pairs, sizeof(uint16_t) * n_pairs, cudaMemcpyHostToDevice, s);   // pageable source: staged before return
+    noalloc_pairs_kernel<<<1, 32, 0, s>>>(pairs_dev, kp0, kp1, c->top_k, MAX_PAIRS);
+    e = cudaGetLastError();
     if (e == cudaSuccess) e = launch_normalize_rows(keys0, c->act_dtype, c->n_keys0, hw, c->norm_keys, 1, khat0, s);
     if (e == cudaSuccess) e = launch_normalize_rows(keys1, c->act_dtype, c->n_keys1, hw, c->norm_keys, 1, khat1, s);
     if (e == cudaSuccess) e = launch_normalize_halves(queries, n_tokens * c->num_heads, c->query_dim, c->norm_query, q_hat, s);

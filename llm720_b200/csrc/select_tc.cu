@@ -1,8 +1,8 @@
 // Product-key selection on the tensor cores (bf16 layers): the two sub-key
 // score contractions run as tcgen05 MMAs with fp32 accumulators in TMEM, and
 // the per-half top-k, the candidate sums, the final top-k, the softmax and
-// the flat expert ids are computed from TMEM with warp-wide votes and
-// reductions.  No score reaches HBM.
+// the flat expert ids are computed from TMEM by the scan warps.  No score
+// reaches HBM.
 //
 // Follows llm/models/experts.py:153-163 (scores), :168-192 (per-half top-k'),
 // :203-259 (candidate sums, flat ids, final top-k) and :327 (softmax).
@@ -16,32 +16,40 @@
 //
 // Layout of the work.  One CTA owns a tile of 128 (token, head) rows at a time
 // (persistent grid).  The accumulator is KEY-major: M = 128 sub-keys (one chunk
-// of the table), N = the 128 rows, so a TMEM lane is a key and a thread that
-// reads 32 columns holds the scores of 32 rows for its key.  A question about
-// one row and 32 keys ("largest score?", "which keys reach the row's bound?")
-// is then ONE warp-wide reduction or vote, with the same control flow in every
-// lane: no lane-dependent branches, no queues, no load imbalance.
+// of the table), N = the 128 rows, so a TMEM lane is a key and a scan thread
+// that reads 32 columns holds the scores of 32 rows for ITS key.
 //
 // Per tile and query half, two passes over the sub-key table (the tensor cores
 // recompute the scores for the second pass; they are otherwise idle):
-//   pass 0  per row, the largest score of every group of 32 keys (redux.max)
-//           -> shared memory; the 16th largest group maximum of a row is a
-//           lower bound of its 16th best score (16 distinct scores reach it)
-//           and typically only about 22 scores of a 1024-key table do;
-//   pass 1  per row and group, a vote "score >= bound"; the few hits are
-//           appended to the row's candidate list in shared memory;
-//   then    one warp per row extracts the 16 best candidates in order.
-// After both halves: candidate sums (a+1)(b+1) <= k, final top-k, softmax, ids,
-// again one warp per row.  Rows whose candidate list overflowed (heavily
-// clustered scores) are written to a list that the exact CUDA-core kernel
-// reprocesses (select_simt.cu), so the result never depends on the heuristic.
+//   pass 0  every lane keeps, per row, the running maximum of its own keys
+//           (one key per chunk); afterwards 4 adjacent lanes are combined with
+//           two shuffles, which gives 32 group maxima per row in shared
+//           memory; the 16th largest of them is a lower bound of the row's
+//           16th best score (16 distinct scores reach it) and typically only
+//           about 22 scores of a 1024-key table reach it;
+//   pass 1  every lane compares its scores with the rows' bounds and notes
+//           its own hits (score into a private shared-memory slot, row into a
+//           bit mask) without votes or branches, then the lanes append their
+//           hits to the rows' candidate lists (shared-memory atomicAdd for the
+//           position); a list longer than CAP continues in a small pool shared
+//           by 32 rows;
+//   then    per row, a bitonic sort of the candidates across the lanes of a
+//           warp (four rows' networks side by side), pool entries inserted
+//           afterwards; the 16 best stay, in order.
+// After both halves: candidate sums (a+1)(b+1) <= k, final top-k by repeated
+// redux.max / redux.min, softmax, ids; four rows per warp side by side.
+// A row that loses a candidate (a lane with more than STAGE_CAP hits in one
+// chunk, or a full pool: heavily clustered scores) is written to a list that
+// the exact CUDA-core kernel reprocesses (select_simt.cu), so the result never
+// depends on the bound heuristic.
 //
-// Warps: 0 = TMA producer, 1 = MMA issuer, 2-3 idle, 4-19 = 16 scan warps
-// (scan warp s reads TMEM lanes 32*(s&3).. and columns 32*(s>>2)..).  The four
-// warps with the same s>>2 produce and consume everything that belongs to
-// their 32 rows (group maxima, bounds, candidate lists, pool), so they
-// synchronise among themselves only (one named barrier per group) and the four
-// groups drift apart by up to the four accumulators in flight.
+// Warps: 0 = TMA producer, 1 = MMA issuer, 2-3 only take part in the set-up
+// and the final barrier, 4-19 = 16 scan warps (scan warp s reads TMEM lanes
+// 32*(s&3).. and columns 32*(s>>2)..).  The four warps with the same s>>2
+// produce and consume everything that belongs to their 32 rows (group maxima,
+// bounds, candidate lists, pool), so they synchronise among themselves only
+// (one named barrier per group) and the four groups drift apart by up to the
+// four accumulators in flight.
 // Ordering among exactly equal scores: smaller sub-key index first (per half),
 // smaller candidate position first (final), as in select_simt.cu.
 #include <float.h>
@@ -97,6 +105,7 @@ struct SelTcParams {
     int32_t* ids32; float* weights; int64_t* ids64; float* raw_scores; int32_t* prod_ids;
     int* status;
     int32_t* overflow_rows; int* overflow_count;   // rows left to the exact kernel
+    unsigned long long* stats;                     // optional [2]: pooled row-halves, rows left to the exact kernel
 };
 
 // order-preserving map fp32 -> int32 (and back): integer compares and redux.max work on scores
@@ -346,7 +355,10 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         const int row = s * 8 + rb + q;
                         const int cnt = s_cnt[row];
                         if (cnt >= LOST) overflow |= 1u << (rb + q);
-                        else if (cnt > CAP) pooled |= 1u << q;
+                        else if (cnt > CAP) {
+                            pooled |= 1u << q;
+                            if (p.stats && lane == 0 && tile * BM + row < p.rows) atomicAdd(p.stats, 1ULL);
+                        }
                         v[q] = -INFINITY; c[q] = INT_MAX;
                         if (lane < min(cnt, CAP)) { const int2 e = s_cand[row * CAP + lane]; v[q] = __int_as_float(e.x); c[q] = e.y; }
                     }
@@ -411,8 +423,10 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 for (int q = 0; q < 4; ++q) {
                     const int64_t grow = tile * BM + s * 8 + rb + q;
                     act[q] = grow < p.rows && !(overflow & (1u << (rb + q)));    // warp-uniform
-                    if (grow < p.rows && (overflow & (1u << (rb + q))) && lane == 0)   // left to the exact kernel
+                    if (grow < p.rows && (overflow & (1u << (rb + q))) && lane == 0) { // left to the exact kernel
                         p.overflow_rows[atomicAdd(p.overflow_count, 1)] = static_cast<int32_t>(grow);
+                        if (p.stats) atomicAdd(p.stats + 1, 1ULL);
+                    }
                     const float s0 = hv[0][q], s1 = hv[1][q];
                     const float v0 = __shfl_sync(FULL_MASK, s0, base + (pa0 & 15)) + __shfl_sync(FULL_MASK, s1, base + (pb0 & 15));
                     const float v1 = __shfl_sync(FULL_MASK, s0, base + (pa1 & 15)) + __shfl_sync(FULL_MASK, s1, base + (pb1 & 15));
@@ -514,7 +528,7 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     p.invn0 = a.invn0; p.invn1 = a.invn1; p.rows = a.rows; p.term_rows = a.term_rows; p.Q = a.Q;
     p.n0 = a.n0; p.n1 = a.n1; p.kp0 = a.kp0; p.kp1 = a.kp1; p.k = a.k; p.mult0 = a.mult0; p.mult1 = a.mult1;
     p.ids32 = a.ids32; p.weights = a.weights; p.ids64 = a.ids64; p.raw_scores = a.raw_scores; p.prod_ids = a.prod_ids; p.status = a.status;
-    p.overflow_rows = a.overflow_rows; p.overflow_count = a.overflow_count;
+    p.overflow_rows = a.overflow_rows; p.overflow_count = a.overflow_count; p.stats = a.stats;
     const int64_t n_tiles = (a.rows + BM - 1) / BM;
     const unsigned grid = static_cast<unsigned>(n_tiles < a.sm_count ? n_tiles : a.sm_count);
     select_tc_kernel<<<grid, THREADS, Smem::total, s>>>(mq, mk0, mk1, p);

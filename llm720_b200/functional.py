@@ -36,9 +36,25 @@ def peer_forward(x: torch.Tensor, query_weight: torch.Tensor, query_bias: Option
     n0, n1 = key_weight_1.shape[0], key_weight_2.shape[0]
     if n0 * n1 != num_experts:
         raise ValueError(f"key tables of {n0} and {n1} rows do not address {num_experts} experts")
+    h = int(expert_hidden_size)
+    if h < 1:
+        raise ValueError(f"expert_hidden_size={expert_hidden_size}")
+    # output width as the reference takes it (peer_cutlass.py:176): dimension 1 of a [N, output_dim, h] table;
+    # a flattened [N, output_dim*h] table (the module's Embedding layout, experts.py:337-352) holds h values per
+    # output column
+    if expert_weights_v.dim() == 3:
+        out_dim = expert_weights_v.shape[1]
+        if expert_weights_v.shape[2] != h:
+            raise ValueError(f"expert_weights_v is {tuple(expert_weights_v.shape)}, expected [N, output_dim, {h}]")
+    else:
+        if expert_weights_v.shape[-1] % h:
+            raise ValueError(f"expert_weights_v rows of {expert_weights_v.shape[-1]} values do not hold {h} neurons")
+        out_dim = expert_weights_v.shape[-1] // h
     u = expert_weights_u.reshape(num_experts, -1)
     v = expert_weights_v.reshape(num_experts, -1)
-    out_dim = v.shape[1]
+    if u.shape[1] != D * h or v.shape[1] != out_dim * h:
+        raise ValueError(f"expert tables of {u.shape[1]} / {v.shape[1]} values per row do not match input_dim {D}, "
+                         f"output_dim {out_dim} and {h} neurons per expert")
     key = (str(x.device), x.dtype, u.dtype, D, out_dim, num_heads, query_dim, n0, n1, top_k, layer_norm,
            index_mode, activation, norm_keys, norm_query, expert_hidden_size)
     T = B * S

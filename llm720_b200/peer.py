@@ -200,6 +200,26 @@ class PeerOp:
                                              _ptr(ids), _ptr(sc), _stream(self.device)))
         return ids, sc
 
+    def select_tokens(self, x: torch.Tensor, w: dict) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Query projection + selection of x [T, D]: (flat expert ids int32, softmax weights fp32), both
+        [T, num_heads*top_k] - the tuples an expert-parallel rank routes to the owners of the rows."""
+        T = x.shape[0]
+        HK = self.cfg.num_heads * self.cfg.top_k
+        ids = torch.empty(T, HK, dtype=torch.int32, device=self.device)
+        wts = torch.empty(T, HK, dtype=torch.float32, device=self.device)
+        t = self._tensors(x, w, None)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_select_tokens(self.handle, C.byref(t), T, _ptr(ids), _ptr(wts), _stream(self.device)))
+        return ids, wts
+
+    def select_stats(self) -> Tuple[int, int]:
+        """(candidate lists that continued in the pool, rows redone by the exact kernel) of the tensor-core
+        selection since the last read; synchronises."""
+        a, b = C.c_int64(0), C.c_int64(0)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_select_stats(self.handle, C.byref(a), C.byref(b), _stream(self.device)))
+        return int(a.value), int(b.value)
+
     def select_nd(self, queries: torch.Tensor, keys) -> Tuple[torch.Tensor, torch.Tensor]:
         """Selection over a key grid of any dimensionality: queries fp32 [T, H, Q] (after LayerNorm), keys a
         sequence of num_key_dims tables -> (ids int64, raw scores fp32) [T, H, k]."""
@@ -340,6 +360,10 @@ class PEER(nn.Module):
       ``_last_expert_scores`` (raw scores, fp32).
     * ``max_slice_tokens``: token capacity of the scratch; longer inputs run in
       slices.
+    * ``table_grad_sums``: ``"fp32"`` (default: the backward pass sums each table
+      row's gradient in fp32 and rounds once, like the reference's embedding
+      backward) or ``"table"`` (bf16 layers: sums formed in bf16, half the
+      traffic, for batches in which few tokens share a row).
     """
 
     def __init__(self, input_dim: int, output_dim: int, num_experts: int, num_experts_per_tok: int = 16,
@@ -387,6 +411,7 @@ class PEER(nn.Module):
         self.index_mode = "reference"
         self.track_indices = True
         self.max_slice_tokens = 16384
+        self.table_grad_sums = "fp32"
         self._last_expert_indices: Optional[torch.Tensor] = None
         self._last_expert_scores: Optional[torch.Tensor] = None
         self._op: Optional[PeerOp] = None
@@ -544,9 +569,13 @@ class PEER(nn.Module):
         return self._forward_host(hidden_states, out, blocking=True)[0]
 
     def forward_host_wait(self, ticket) -> None:
-        """Block until the batch submitted by ``forward_host_async`` has landed in its host output."""
-        op, tk = ticket
+        """Block until the batch submitted by ``forward_host_async`` has landed in its host output.  The ticket
+        holds the batch's host buffers (input, output, ids, scores) until here, so none of them can be freed or
+        handed out again while a copy is still queued on the library's streams; the tracker attributes
+        (``_last_expert_indices`` / ``_last_expert_scores``) are set now, when their contents are complete."""
+        op, tk, _x, _out, ids, sc, (B, S) = ticket
         op.forward_host_wait(tk)
+        self._stash(ids, sc, B, S)
 
     def forward_host_async(self, hidden_states: torch.Tensor, out: Optional[torch.Tensor] = None):
         """Submit a host batch without waiting: returns ``(out, ticket)``.  The next batch may be submitted
@@ -566,6 +595,9 @@ class PEER(nn.Module):
             raise RuntimeError("forward_host takes a host tensor")
         B, S, _ = hidden_states.shape
         T = B * S
+        if not blocking and not hidden_states.is_contiguous():
+            # a contiguous copy would be a temporary that dies while its copy-in is still queued
+            raise ValueError("forward_host_async needs a contiguous host tensor")
         x = hidden_states.contiguous().view(T, self.input_dim)
         dev = self.query_proj.weight.device
         op = self._operator(dev, dt, T)
@@ -578,9 +610,9 @@ class PEER(nn.Module):
         ticket = None
         if blocking:
             op.forward_host(x, w, out.view(T, self.output_dim), ids, sc)
+            self._stash(ids, sc, B, S)
         else:
-            ticket = (op, op.forward_host_async(x, w, out.view(T, self.output_dim), ids, sc))
-        self._stash(ids, sc, B, S)          # complete after the wait
+            ticket = (op, op.forward_host_async(x, w, out.view(T, self.output_dim), ids, sc), x, out, ids, sc, (B, S))
         return out, ticket
 
     def _stash(self, ids, sc, B, S):
@@ -604,3 +636,12 @@ class PEER(nn.Module):
         return ids.view(B, S, H, -1), sc.view(B, S, H, -1).to(queries.dtype)
 
     _get_expert_indices = select
+    # the name the reference's own selection test calls (tests/test_peer_selection.py:123)
+    _get_expert_indices_pytorch = select
+
+    def split_queries(self, queries: torch.Tensor) -> List[torch.Tensor]:
+        """One slice of the last dimension per key dimension, in order (experts.py:125-136): views of
+        ``queries[..., d*w:(d+1)*w]`` with ``w = query_dim // len(product_key_dim)``.  The kernels do this split
+        inside the query epilogue; the method exists for callers of the reference's API."""
+        w = self.query_dim // len(self.product_key_dim)
+        return [queries[..., d * w:(d + 1) * w] for d in range(len(self.product_key_dim))]

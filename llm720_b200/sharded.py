@@ -17,8 +17,11 @@ the layer for tables that do not fit, or should not be replicated, on every GPU:
   5. reduce-scatter of the partial sums gives every rank the outputs of its own tokens.
 
 Result: identical to the single-device layer on the concatenated batch, up to fp32 summation
-order.  The exchange logic (`route_tuples`, `pack_received`) is plain tensor code that runs on
-any device, so it is tested with CPU ranks over gloo; the kernels run on CUDA only.
+order.  The exchange logic exists twice: as plain tensor code (`route_tuples*`, `pack_received*`)
+that runs on any device and is tested with CPU ranks over gloo, and as two kernels of the library
+(`peer_route_tuples`, `peer_pack_tuples`, wrapped by `route_tuples_native` / `pack_received_native`)
+that `ShardedPEER` uses on the GPU: one launch each instead of some twenty-five small tensor
+operations, same buckets and lists (a GPU test compares the two forms).
 """
 from __future__ import annotations
 
@@ -134,6 +137,49 @@ def pack_received_static(recv: torch.Tensor, n_tokens: int, cap: int):
     return ids[:n_tokens], w[:n_tokens], torch.clamp(counts[:n_tokens], max=cap).to(torch.int32)
 
 
+def route_tuples_native(ids32: torch.Tensor, weights: torch.Tensor, token_offset: int, rows: int, world: int,
+                        send: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """`route_tuples_static` as one kernel (CUDA tensors): ids int32 [T, HK], weights fp32 [T, HK] ->
+    int32 [world, T*HK, 3]; a bucket keeps (token, slot) order, padding carries token -1."""
+    import ctypes as C
+    from . import _lib
+    T, HK = ids32.shape
+    if ids32.dtype != torch.int32 or weights.dtype != torch.float32 or not ids32.is_cuda:
+        raise TypeError("route_tuples_native takes CUDA tensors: int32 ids and fp32 weights")
+    if send is None:
+        send = torch.empty(world, T * HK, 3, dtype=torch.int32, device=ids32.device)
+    lib = _lib.load()
+    with torch.cuda.device(ids32.device):
+        rc = lib.peer_route_tuples(C.c_void_p(ids32.contiguous().data_ptr()), C.c_void_p(weights.contiguous().data_ptr()),
+                                   T, HK, int(token_offset), int(rows), int(world), T * HK, C.c_void_p(send.data_ptr()),
+                                   C.c_void_p(torch.cuda.current_stream(ids32.device).cuda_stream))
+    _lib.check(rc, None)
+    return send
+
+
+def pack_received_native(recv: torch.Tensor, n_tokens: int, cap: int, out=None):
+    """`pack_received_static` as one kernel: buckets int32 [world, m, 3] -> (ids int32 [T, cap], weights fp32
+    [T, cap], counts int32 [T]), lists in (source rank, position) order."""
+    import ctypes as C
+    from . import _lib
+    if recv.dtype != torch.int32 or not recv.is_cuda or not recv.is_contiguous():
+        raise TypeError("pack_received_native takes a contiguous CUDA int32 tensor")
+    world, m, _ = recv.shape
+    dev = recv.device
+    if out is None:
+        out = (torch.empty(n_tokens, cap, dtype=torch.int32, device=dev),
+               torch.empty(n_tokens, cap, dtype=torch.float32, device=dev),
+               torch.empty(n_tokens, dtype=torch.int32, device=dev))
+    ids, w, cnt = out
+    lib = _lib.load()
+    with torch.cuda.device(dev):
+        rc = lib.peer_pack_tuples(C.c_void_p(recv.data_ptr()), int(world), int(m), int(n_tokens), int(cap),
+                                  C.c_void_p(ids.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(cnt.data_ptr()),
+                                  C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
+    _lib.check(rc, None)
+    return ids, w, cnt
+
+
 def reduce_scatter_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
     """[T_total, D] fp32 partial sums -> this rank's [T_total/world, D] slice of the sum."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
@@ -178,6 +224,7 @@ class ShardedPEER:
 
     def __init__(self, layer, group=None):
         self.layer, self.group = layer, group
+        self._buf, self._buf_key, self.last_counts = None, None, None
         self.world = dist.get_world_size(group)
         self.rows = rows_per_rank(layer.num_experts, self.world)
         if layer.expert_down.weight.shape[0] != self.rows:
@@ -202,23 +249,50 @@ class ShardedPEER:
 
     @torch.no_grad()
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        """[B, S, D] of THIS rank's tokens (the same B*S on every rank) -> [B, S, D_out].  Per step: three
+        NCCL collectives (all-gather of x, all-to-all of the tuple buckets, reduce-scatter of the fp32
+        partial sums) and the library's kernels between them: query + selection, routing, packing, partial
+        expert evaluation.  Buffers are kept between calls of the same shape."""
         L = self.layer
         B, S, D = hidden_states.shape
-        x = hidden_states.contiguous().view(B * S, D)
+        T = B * S
+        world, rank = self.world, dist.get_rank(self.group)
+        x = hidden_states.contiguous().view(T, D)
         w = L._weights()
-        op = L._operator(x.device, x.dtype, B * S * self.world)
-
-        def select_fn(xl):
-            q = op.project_queries(xl, w)
-            ids, raw = op.select(q, w["keys0"], w["keys1"])
-            T = xl.shape[0]
-            return ids.view(T, -1), torch.softmax(raw, dim=-1).view(T, -1)
-
-        def eval_fn(x_all, p_ids, p_w, p_cnt):
-            return op.gather_eval_partial(x_all, p_ids.contiguous(), p_w.contiguous(), p_cnt, w["expert_down"],
-                                          w["expert_up"], w["down_scale"], w["up_scale"])
-
-        out = sharded_forward(x, select_fn, eval_fn, L.num_experts, self.group)
+        op = L._operator(x.device, x.dtype, T * world)
+        HK = L.num_heads * L.num_experts_per_tok
+        key = (T, D, x.dtype, str(x.device))
+        if self._buf_key != key:
+            dev = x.device
+            self._buf = dict(
+                x_all=torch.empty(world * T, D, dtype=x.dtype, device=dev),
+                send=torch.empty(world, T * HK, 3, dtype=torch.int32, device=dev),
+                recv=torch.empty(world, T * HK, 3, dtype=torch.int32, device=dev),
+                lists=(torch.empty(world * T, HK, dtype=torch.int32, device=dev),
+                       torch.empty(world * T, HK, dtype=torch.float32, device=dev),
+                       torch.empty(world * T, dtype=torch.int32, device=dev)))
+            self._buf_key = key
+        b = self._buf
+        dist.all_gather_into_tensor(b["x_all"], x, group=self.group)
+        ids, wts = op.select_tokens(x, w)
+        route_tuples_native(ids, wts, rank * T, self.rows, world, b["send"])
+        dist.all_to_all_single(b["recv"], b["send"], group=self.group)
+        p_ids, p_w, p_cnt = pack_received_native(b["recv"], world * T, HK, b["lists"])
+        partial = op.gather_eval_partial(b["x_all"], p_ids, p_w, p_cnt, w["expert_down"], w["expert_up"],
+                                         w["down_scale"], w["up_scale"])
+        self.last_counts = p_cnt                  # tuples this rank evaluated, per token (device tensor)
+        out = reduce_scatter_rows(partial, self.group)
         return out.to(hidden_states.dtype).view(B, S, -1)
+
+    def nvlink_bytes_per_step(self, tokens_per_rank: int) -> dict:
+        """Bytes each rank SENDS per step, by collective (fixed-shape buckets: the all-to-all carries
+        the padded capacity, not only the tuples in use)."""
+        L, G, T = self.layer, self.world, tokens_per_rank
+        HK = L.num_heads * L.num_experts_per_tok
+        eb = L.query_proj.weight.element_size()
+        return {"all_gather_x": (G - 1) * T * L.input_dim * eb,
+                "all_to_all_buckets": (G - 1) * T * HK * 12,
+                "all_to_all_tuples_in_use": (G - 1) * T * HK * 12 // G,
+                "reduce_scatter_partials_fp32": (G - 1) * T * L.output_dim * 4}
 
     __call__ = forward

@@ -96,3 +96,12 @@ def test_block_forward_argument_checks(cuda_device):
         m.block_forward(x, ln)
     with pytest.raises(RuntimeError, match="inference path"):
         m.block_forward(x, ln)
+
+
+def test_three_blocks_chained_against_the_oracle(cuda_device):
+    """The twelve-layer PEER stack of the benchmark, at a size the oracle finishes in seconds: three
+    blocks h + PEER(ln_2(h)) in a row, every block checked against the oracle on the block's own input
+    (the same check the benchmark line reports as extra.c5_peer_stack.parity)."""
+    import bench
+    ok, (mx, l1) = bench._stack_parity(cuda_device)
+    assert ok, (mx, l1)

@@ -10,7 +10,7 @@ import numpy as np
 import pytest
 import torch
 
-from llm720_b200 import PEER, synthetic as syn
+from llm720_b200 import PEER, peer_forward_cutlass, synthetic as syn
 from oracle import peer_oracle as orc
 from _util import (GENERAL_CASES, general_oracle_weights, load_general, load_golden, make_op, oracle_shape,
                    oracle_weights, rel_err)
@@ -88,6 +88,27 @@ def test_general_selection_against_the_oracle(cuda_device, grid, Q, k, H, dtype,
     if len(grid) == 2:        # the specialised kernel gives the same lists
         ids2, sc2 = op.select(q.view(130, H, Q).to(cuda_device).contiguous(), keys[0].to(cuda_device), keys[1].to(cuda_device))
         _check_ids(ids2.view(1, 130, H, k), ref_ids, ref_sc, sc2.view(1, 130, H, k))
+
+
+@pytest.mark.parametrize("three_d", [False, True])
+def test_functional_entry_with_several_neurons_per_expert(cuda_device, three_d):
+    """peer_forward_cutlass with expert_hidden_size = 8: the output width is that of the reference wrapper
+    (peer_cutlass.py:176: dimension 1 of a [N, output_dim, h] table), also when the table comes flattened as
+    the module stores it ([N, output_dim*h])."""
+    cfg, sd, x, rec = load_general("h8_fp32")
+    g = lambda k: sd[k].to(cuda_device)
+    h, N = cfg.expert_hidden_size, cfg.num_experts
+    u, v = g("expert_down.weight"), g("expert_up.weight")
+    if three_d:
+        u, v = u.view(N, h, cfg.input_dim), v.view(N, cfg.output_dim, h)
+    y = peer_forward_cutlass(x.to(cuda_device), g("query_proj.weight"), g("query_proj.bias"), g("sub_keys.0"),
+                             g("sub_keys.1"), u, v, cfg.num_heads, N, h, cfg.top_k, layer_norm=False)
+    assert y.shape == (cfg.batch, cfg.seq, cfg.output_dim)
+    assert rel_err(y.cpu(), torch.from_numpy(rec["out"])) < 2e-5
+    with pytest.raises(ValueError, match="neurons"):
+        peer_forward_cutlass(x.to(cuda_device), g("query_proj.weight"), g("query_proj.bias"), g("sub_keys.0"),
+                             g("sub_keys.1"), u.reshape(N, -1), v.reshape(N, -1)[:, :-1].contiguous(), cfg.num_heads, N, h,
+                             cfg.top_k, layer_norm=False)
 
 
 def test_reference_test_layer_in_bf16(cuda_device):

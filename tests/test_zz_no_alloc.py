@@ -12,6 +12,7 @@ import pytest
 import torch
 
 from llm720_b200 import _lib, synthetic as syn
+from oracle import peer_oracle as orc
 from _util import make_op
 
 pytestmark = pytest.mark.gpu
@@ -48,6 +49,12 @@ def test_noalloc_select_equals_handle_select_twice(cuda_device, mode):
         torch.cuda.synchronize()
         assert torch.equal(ids, want_ids)      # same kernels, same inputs: bit-identical
         assert torch.equal(sc, want_sc)
+        # and directly against the oracle's selection (experts.py:138-285 restated), near ties aside
+        with torch.no_grad():
+            o_ids, o_sc = orc.select(q.cpu().unsqueeze(0), [k0.cpu(), k1.cpu()], k, (n, n), index_mode=mode)
+        rows, exact, near, bad = orc.compare_selection(ids.cpu(), o_ids.view(ids.shape), o_sc.view(sc.shape), sc.cpu())
+        assert bad == 0 and exact >= 0.99 * rows
+        assert torch.allclose(sc.cpu(), o_sc.view(sc.shape), rtol=0, atol=3e-6)
 
 
 def test_noalloc_select_refuses_what_does_not_fit(cuda_device):
