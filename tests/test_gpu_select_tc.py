@@ -83,7 +83,7 @@ def test_identical_keys_overflow_the_list_into_the_pool(cuda_device):
     T, H, Q, n, k = 96, 2, 256, 1024, 16
     keys = [_keys(n, Q // 2, 11), _keys(n, Q // 2, 12)]
     dup = torch.arange(40) * 25 + 3                              # 40 rows of table 0, many key groups
-    keys[0][dup] = keys[0][3]
+    keys[0][dup] = keys[0][3].clone()
     q = _queries(T, H, Q, 13)
     hot = torch.arange(0, T, 9)                                   # a few rows per tile: the pool (64 entries) suffices
     q[hot, :, :Q // 2] = q[hot, :, :Q // 2] * 0.3 + 4.0 * keys[0][3].float()
@@ -98,7 +98,7 @@ def test_hundreds_of_identical_keys_fill_the_pool_and_rows_are_redone_exactly(cu
     T, H, Q, n, k = 40, 4, 256, 1024, 16
     keys = [_keys(n, Q // 2, 21), _keys(n, Q // 2, 22)]
     dup = torch.arange(300) * 3 + 1
-    keys[1][dup] = keys[1][1]
+    keys[1][dup] = keys[1][1].clone()
     q = _queries(T, H, Q, 23)
     q[:, :, Q // 2:] = q[:, :, Q // 2:] * 0.3 + 4.0 * keys[1][1].float()      # every row ties 300 ways
     ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k)
@@ -112,7 +112,7 @@ def test_a_popular_key_exceeds_one_lanes_staging_slots(cuda_device):
     T, H, Q, n, k = 64, 2, 128, 512, 8
     keys = [_keys(n, Q // 2, 31), _keys(n, Q // 2, 32)]
     q = _queries(T, H, Q, 33)
-    q[:, :, :Q // 2] += 2.0 * keys[0][77].float() * (Q // 2) ** 0.5 * 0.2
+    q[:, :, :Q // 2] += 6.0 * keys[0][77].float()            # cosine with key 77 around 0.6 in every row
     ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k)
     assert refined > 0, "the staging-slot overflow did not fire"
     assert float(((ids // n) == 77).any(-1).float().mean()) > 0.9
