@@ -166,6 +166,7 @@ struct GatherParams {
     const int32_t* counts;     // optional [T]: entries of token t that are in use (<= HK)
     float* out_f32;            // optional [T, Dout] fp32 output instead of `out`
     const void* residual;      // optional [T, Dout] in the activation dtype, added to the result
+    int split;                 // the warps of a CTA share one token (few tokens: decode-shaped batches)
 };
 
 template <typename XT, typename TT, int CH, bool W10>
@@ -205,15 +206,23 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
     uint32_t parity = 0;     // its phase
     bool alive = true;
 
+    // Two ways to spread the work.  Ordinarily every warp owns a token.  With few tokens (split) the WARPS warps
+    // of a CTA share one: warp w takes the token's entries w, w + WARPS, ... and the partial sums meet in shared
+    // memory at the end, added in warp order, so the result does not depend on timing.
     const int64_t nwarps = static_cast<int64_t>(gridDim.x) * WARPS;
-    for (int64_t t = static_cast<int64_t>(blockIdx.x) * WARPS + warp; t < p.T && alive; t += nwarps) {
+    const int64_t t_first = p.split ? static_cast<int64_t>(blockIdx.x) : static_cast<int64_t>(blockIdx.x) * WARPS + warp;
+    const int64_t t_step = p.split ? static_cast<int64_t>(gridDim.x) : nwarps;
+    for (int64_t t = t_first; t < p.T && (alive || p.split); t += t_step) {
         // ---- token prologue: selections into shared memory, x into registers
         __syncwarp();
-        const int hk = p.counts ? min(max(p.counts[t], 0), p.HK) : p.HK;
+        const int hk_token = p.counts ? min(max(p.counts[t], 0), p.HK) : p.HK;
+        // entries of this warp: all of the token's, or every WARPS-th one starting at `warp`
+        const int e_first = p.split ? warp : 0, e_step = p.split ? WARPS : 1;
+        const int hk = p.split ? (hk_token > warp ? (hk_token - warp + WARPS - 1) / WARPS : 0) : hk_token;
         const int total_rows = 2 * hk;
         for (int e = lane; e < hk; e += 32) {
-            int32_t id = p.ids[t * p.HK + e];
-            float w = p.weights[t * p.HK + e];
+            int32_t id = p.ids[t * p.HK + e_first + e * e_step];
+            float w = p.weights[t * p.HK + e_first + e * e_step];
             if (static_cast<uint32_t>(id) >= static_cast<uint64_t>(p.N)) {
                 atomicMax(p.status, STATUS_BOUNDS);
                 id = 0; w = 0.f;
@@ -286,7 +295,7 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             mbar_expect_tx(bars_a + 8 * s, bytes);
             bulk_g2s(ring_a + s * SLOT, src, bytes, bars_a + 8 * s);
         };
-        if (lane == 0) {
+        if (lane == 0 && alive) {
             int s = slot;
             for (int r = 0; r < STAGES && r < total_rows; ++r) {
                 issue(r, s);
@@ -294,7 +303,7 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             }
         }
 
-        for (int e = 0; e < hk; ++e) {
+        for (int e = 0; e < hk && alive; ++e) {
             // ---- down row: dot with x
             if (!mbar_wait(bars_a + 8 * slot, parity, p.status)) { alive = false; }
             alive = __all_sync(FULL_MASK, alive);
@@ -359,6 +368,34 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             if (lane == 0 && 2 * e + 1 + STAGES < total_rows) issue(2 * e + 1 + STAGES, slot);
             if (++slot == STAGES) { slot = 0; parity ^= 1; }
         }
+        if (p.split) {
+            // every warp of the CTA comes here, also one whose wait ran out (its sums are dropped with the status
+            // word set): the partial sums go to shared memory - the rings are idle now - and are added in warp order
+            __syncthreads();
+            float* part = reinterpret_cast<float*>(smem);                 // [WARPS][Dout]
+#pragma unroll
+            for (int i = 0; i < CH; ++i) {
+                const int c = lane + 32 * i;
+                if (c < p.nch_v) {
+#pragma unroll
+                    for (int q = 0; q < EPC; q += 4)
+                        *reinterpret_cast<float4*>(part + static_cast<size_t>(warp) * p.Dout + c * EPC + q) =
+                            make_float4(acc[i * EPC + q], acc[i * EPC + q + 1], acc[i * EPC + q + 2], acc[i * EPC + q + 3]);
+                }
+            }
+            __syncthreads();
+            for (int col = threadIdx.x; col < p.Dout; col += WARPS * 32) {
+                float sum = 0.f;
+                for (int w = 0; w < WARPS; ++w) sum += part[static_cast<size_t>(w) * p.Dout + col];
+                if (p.out_f32) p.out_f32[t * p.Dout + col] = sum;
+                else {
+                    if (p.residual) sum += to_f32<XT>(static_cast<const XT*>(p.residual)[t * p.Dout + col]);
+                    og[t * p.Dout + col] = from_f32<XT>(sum);
+                }
+            }
+            __syncthreads();                                              // before the rings are filled again
+            continue;
+        }
         if (!alive) break;
 
 #pragma unroll
@@ -413,7 +450,15 @@ cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
     constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
     int64_t ctas = (a.T + WARPS - 1) / WARPS;
     if (ctas > a.sm_count) ctas = a.sm_count;
-    gather_eval_kernel<XT, TT, CH, W10><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(p);
+    GatherParams q = p;
+    // few tokens (a decode-shaped batch): one token per CTA, its entries dealt to the warps, so that all SMs
+    // stream rows instead of T / WARPS of them; the partial sums need WARPS * Dout floats of the ring space
+    // (only for the partial evaluation of a row shard: the ordinary layer keeps one warp per token at every batch
+    // size, so that a token's result never depends on how many tokens came with it)
+    q.split = a.counts != nullptr && a.T <= a.sm_count &&
+              static_cast<size_t>(WARPS) * a.Dout * sizeof(float) <= static_cast<size_t>(WARPS) * RingCfg<TT, CH, W10>::STAGES * RingCfg<TT, CH, W10>::SLOT;
+    if (q.split) ctas = a.T;
+    gather_eval_kernel<XT, TT, CH, W10><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(q);
     return cudaGetLastError();
 }
 
@@ -451,7 +496,7 @@ cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
     p.down_scale = a.down_scale; p.up_scale = a.up_scale; p.out = a.out; p.T = a.T; p.HK = a.HK;
     p.N = a.N; p.D = a.D; p.Dout = a.Dout; p.activation = a.activation; p.status = a.status;
     p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
-    p.counts = a.counts; p.out_f32 = a.out_f32; p.residual = a.residual;
+    p.counts = a.counts; p.out_f32 = a.out_f32; p.residual = a.residual; p.split = 0;
     const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
     if (a.act_dtype == PEER_DTYPE_F32 && a.table_dtype == PEER_DTYPE_F32)
         return launch_ch<float, float>(a, p, max_ch, s);

@@ -39,6 +39,7 @@ struct peer_op {
     int32_t* ovf_rows = nullptr;  // [max_tokens*H] rows the tensor-core select leaves to the exact kernel
     int* ovf_count = nullptr;
     unsigned long long* sel_stats = nullptr;   // [2] accumulated: pooled row-halves, rows redone by the exact kernel
+    float* sel_eps = nullptr;                  // [2] error bound of the select kernel's two-term first pass, per table
     void* x_ln = nullptr;         // [max_tokens, D] act dtype: LayerNorm of the block input (peer_block_forward)
     int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
     float* sel_w = nullptr;       // [max_tokens, H*k]
@@ -103,7 +104,7 @@ static int candidates_per_dim(int top_k, int dim_size, int num_dims = 2) {
 namespace peer { int candidates_per_dim_2d(int top_k, int dim_size) { return candidates_per_dim(top_k, dim_size); } }
 
 static void free_all(peer_op* h) {
-    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->ovf_rows); cudaFree(h->ovf_count); cudaFree(h->sel_stats); cudaFree(h->sel_ids);
+    cudaFree(h->khat0); cudaFree(h->khat1); cudaFree(h->q_hat); cudaFree(h->q_split); cudaFree(h->invn0); cudaFree(h->invn1); cudaFree(h->ovf_rows); cudaFree(h->ovf_count); cudaFree(h->sel_stats); cudaFree(h->sel_eps); cudaFree(h->sel_ids);
     cudaFree(h->sel_w); cudaFree(h->pairs); cudaFree(h->status); cudaFree(h->x_ln);
     for (int b = 0; b < 2; ++b) {
         cudaFree(h->d_x[b]); cudaFree(h->d_out[b]); cudaFree(h->d_ids[b]); cudaFree(h->d_sc[b]);
@@ -268,6 +269,8 @@ extern "C" int peer_create(const peer_config_t* c, peer_handle_t* out) {
         alloc(reinterpret_cast<void**>(&h->ovf_rows), sizeof(int32_t) * c->max_tokens * c->num_heads);
         alloc(reinterpret_cast<void**>(&h->ovf_count), sizeof(int));
         alloc(reinterpret_cast<void**>(&h->sel_stats), 2 * sizeof(unsigned long long));
+        if (c->norm_query)          // the two-term first pass needs unit queries for its error bound
+            alloc(reinterpret_cast<void**>(&h->sel_eps), 2 * sizeof(float));
         if (e == cudaSuccess) e = cudaMemset(h->sel_stats, 0, 2 * sizeof(unsigned long long));
     }
     if (h->use_tc)
@@ -330,8 +333,8 @@ static int normalise_keys(peer_op* h, const void* keys0, const void* keys1, cuda
 static int key_inv_norms(peer_op* h, const void* keys0, const void* keys1, cudaStream_t s) {
     const peer_config_t& c = h->cfg;
     const int hw = c.query_dim / 2;
-    CU_TRY(h, launch_key_inv_norms(keys0, c.n_keys0, hw, c.norm_keys, h->invn0, s));
-    CU_TRY(h, launch_key_inv_norms(keys1, c.n_keys1, hw, c.norm_keys, h->invn1, s));
+    CU_TRY(h, launch_key_inv_norms(keys0, c.n_keys0, hw, c.norm_keys, h->invn0, s, h->sel_eps));
+    CU_TRY(h, launch_key_inv_norms(keys1, c.n_keys1, hw, c.norm_keys, h->invn1, s, h->sel_eps ? h->sel_eps + 1 : nullptr));
     h->launches += 2;
     return PEER_OK;
 }
@@ -359,6 +362,7 @@ static int select_tc_slice(peer_op* h, const void* keys0, const void* keys1, int
     ta.ids64 = ids_out; ta.raw_scores = scores_out; ta.status = h->status; ta.sm_count = h->sm_count;
     ta.prod_ids = prod_out;
     ta.overflow_rows = h->ovf_rows; ta.overflow_count = h->ovf_count; ta.stats = h->sel_stats;
+    if (h->sel_eps) { ta.eps0 = h->sel_eps; ta.eps1 = h->sel_eps + 1; }
     CU_TRY(h, cudaMemsetAsync(h->ovf_count, 0, sizeof(int), s));
     CU_TRY(h, launch_select_tc(ta, s));
     SelectArgs fx = select_args(h, n);

@@ -20,7 +20,18 @@
 // that reads 32 columns holds the scores of 32 rows for ITS key.
 //
 // Per tile and query half, two passes over the sub-key table (the tensor cores
-// recompute the scores for the second pass; they are otherwise idle):
+// recompute the scores for the second pass; they are otherwise idle).  The
+// first pass only has to produce a LOWER BOUND of each row's 16th best score,
+// so with normalised queries it contracts two of the three bf16 terms of the
+// query (hi + mid): two thirds of the MMAs.  Dropping lo changes a score by at
+// most eps = 2^-16 ||k|| / max(||k||, 1e-12) (Cauchy-Schwarz with ||q|| = 1; hi and
+// mid each leave a relative remainder of 2^-8 per element; key_inv_norm_kernel
+// takes the maximum over the table), and 16 distinct keys reach the 16th
+// largest group maximum t of those scores, so the exact 16th best score is at
+// least t - eps: that is the bound the exact second pass collects against.
+// (One term and sub-keys rounded to bf16 after normalisation, a third of the
+// MMAs and no scaling, was measured too: its eps of 6e-3 adds three candidates
+// per row, enough list overflows to cost more than the MMAs saved.)
 //   pass 0  every lane keeps, per row, the running maximum of its own keys
 //           (one key per chunk); afterwards 4 adjacent lanes are combined with
 //           two shuffles, which gives 32 group maxima per row in shared
@@ -77,6 +88,7 @@ constexpr int SCAN_WARPS = 16;
 constexpr int POOL = 64;           // candidates beyond CAP, per group of 32 rows (4 such pools per tile)
 constexpr int LOST = 1 << 20;      // added to a row's count when one of its candidates could not be kept
 constexpr int STAGE_CAP = 8;       // scores a lane can hold back per chunk before they go to the row lists
+constexpr int GMAX_PITCH = 33;     // floats per key group in a row group's block of maxima (32 rows + 1: no bank conflicts)
 constexpr int THREADS = 128 + SCAN_WARPS * 32;
 constexpr int CTRL_REGS = 24, SCAN_REGS = 112;     // 128*24 + 512*112 <= 640*96 registers at launch
 constexpr uint32_t TMEM_COLS = 512;
@@ -85,17 +97,20 @@ constexpr int KEY_MIN = INT_MIN;   // ordered-int image of "no score"
 struct Smem {
     static constexpr size_t q_off = 0;
     static constexpr size_t k_off = q_off + Q_BYTES;
-    static constexpr size_t gmax_off = k_off + static_cast<size_t>(K_STAGES) * K_STAGE_BYTES;   // [MAX_GROUPS][128] int
-    static constexpr size_t cand_off = gmax_off + MAX_GROUPS * BM * 4;                           // [128][CAP] (key, col)
+    // group maxima, one block per group of 32 rows (= per set of four scan warps): [4][MAX_GROUPS][GMAX_PITCH] float.
+    // The same block serves its four warps as staging slots in pass 1 ([STAGE_CAP][128] float), when their own
+    // group maxima are dead.  Blocks of different row groups never overlap: the four sets of warps run up to
+    // N_ACC accumulators apart, so one may be in pass 1 while another still reads its group maxima.
+    static constexpr size_t gmax_off = k_off + static_cast<size_t>(K_STAGES) * K_STAGE_BYTES;
+    static constexpr size_t cand_off = gmax_off + 4 * MAX_GROUPS * GMAX_PITCH * 4;               // [128][CAP] (key, col)
     static constexpr size_t cnt_off = cand_off + BM * CAP * 8;                                   // [128] int
     static constexpr size_t tau_off = cnt_off + BM * 4;                                          // [128] int
-    static constexpr size_t stage_off = gmax_off;          // [STAGE_CAP][512] float: pass 1 only, when the group maxima are dead
     static constexpr size_t pool_off = tau_off + BM * 4;                                         // [POOL] (row, score, sub-key, -)
     static constexpr size_t bar_off = pool_off + 4 * POOL * 16;
     static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 32 + 1008;
 };
 static_assert(Smem::total <= 227 * 1024, "shared memory budget");
-static_assert(STAGE_CAP * SCAN_WARPS * 32 * 4 <= MAX_GROUPS * BM * 4, "the staging slots reuse the group maxima");
+static_assert(STAGE_CAP * 128 <= MAX_GROUPS * GMAX_PITCH, "a row group's staging slots reuse its own group maxima");
 
 struct SelTcParams {
     const float* invn0; const float* invn1;   // 1/||key|| per sub-key (or 1)
@@ -106,6 +121,8 @@ struct SelTcParams {
     int* status;
     int32_t* overflow_rows; int* overflow_count;   // rows left to the exact kernel
     unsigned long long* stats;                     // optional [2]: pooled row-halves, rows left to the exact kernel
+    int fast0;                                     // pass 0 contracts two query terms instead of three
+    const float* eps0; const float* eps1;          // fast0: largest error of such a score, per table (device scalars)
 };
 
 // order-preserving map fp32 -> int32 (and back): integer compares and redux.max work on scores
@@ -122,11 +139,10 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    float* s_gmax = reinterpret_cast<float*>(smem + Smem::gmax_off); // [group][row]
+    float* s_gmax = reinterpret_cast<float*>(smem + Smem::gmax_off); // [row group][key group][GMAX_PITCH]
     int2* s_cand = reinterpret_cast<int2*>(smem + Smem::cand_off);   // [row][CAP] (score key, sub-key index)
     int* s_cnt = reinterpret_cast<int*>(smem + Smem::cnt_off);
     float* s_tau = reinterpret_cast<float*>(smem + Smem::tau_off);
-    float* s_stage = reinterpret_cast<float*>(smem + Smem::stage_off);
     int4* s_pool = reinterpret_cast<int4*>(smem + Smem::pool_off);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Smem::bar_off);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
@@ -207,7 +223,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         tc::fence_after_sync();
                         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * BM;
                         uint32_t first = 0;
-                        for (int t = 0; t < 3; ++t)
+                        const int terms = (c < nch && p.fast0) ? 2 : 3;     // pass 0 of the fast form: hi + mid
+                        for (int t = 0; t < terms; ++t)
                             for (int ka = 0; ka < KA; ++ka) {
                                 const uint64_t kd = tc::smem_desc_sw128(sK + stage * K_STAGE_BYTES + ka * BOX_BYTES);
                                 const uint64_t qd = tc::smem_desc_sw128(sQ + (t * KA + ka) * BOX_BYTES);
@@ -271,8 +288,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             // Every lane notes its own hits (score into a private slot, row into a bit
                             // mask) without votes or branches, then the lanes append their hits to the
                             // rows' lists side by side.
-                            float* slot = s_stage + (s * 32 + lane);
-                            constexpr uint32_t SLOT_STEP = SCAN_WARPS * 32 * 4;          // bytes between a lane's slots
+                            float* slot = s_gmax + cg * (MAX_GROUPS * GMAX_PITCH) + quarter * 32 + lane;   // this row group's block
+                            constexpr uint32_t SLOT_STEP = 128 * 4;                      // bytes between a lane's slots
                             uint32_t addr = smem_u32(slot);
                             const uint32_t last = addr + (STAGE_CAP - 1) * SLOT_STEP;
                             unsigned myhits = 0;
@@ -292,7 +309,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                     const int row = cg * 32 + __ffs(myhits) - 1;
                                     myhits &= myhits - 1;
                                     if (taken < STAGE_CAP - 1 || nh <= STAGE_CAP) {
-                                        const float x = slot[taken * (SCAN_WARPS * 32)];
+                                        const float x = slot[taken * 128];
                                         const int pos = atomicAdd(&s_cnt[row], 1);
                                         if (pos < CAP) {
                                             s_cand[row * CAP + pos] = make_int2(__float_as_int(x), key);
@@ -315,7 +332,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         for (int j = 0; j < 32; ++j) {
                             float m = fmaxf(bnd[j], __shfl_xor_sync(FULL_MASK, bnd[j], 1));
                             m = fmaxf(m, __shfl_xor_sync(FULL_MASK, m, 2));
-                            if ((lane & 3) == 0) s_gmax[(quarter * 8 + (lane >> 2)) * BM + cg * 32 + j] = m;
+                            if ((lane & 3) == 0) s_gmax[(cg * MAX_GROUPS + quarter * 8 + (lane >> 2)) * GMAX_PITCH + j] = m;
                         }
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
@@ -324,7 +341,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         // (the 8 rows' sorting networks are written side by side so their shuffles overlap)
                         float tv[8];
 #pragma unroll
-                        for (int rr = 0; rr < 8; ++rr) tv[rr] = s_gmax[lane * BM + s * 8 + rr];
+                        for (int rr = 0; rr < 8; ++rr) tv[rr] = s_gmax[(cg * MAX_GROUPS + lane) * GMAX_PITCH + quarter * 8 + rr];
 #pragma unroll
                         for (int k = 2; k <= 32; k <<= 1)
 #pragma unroll
@@ -336,9 +353,11 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                     tv[rr] = keep_max ? fmaxf(tv[rr], o) : fminf(tv[rr], o);
                                 }
                             }
+                        // fast form: the group maxima lack the lo term; the exact 16th best score is at least t - eps
+                        const float eps = p.fast0 ? __ldg(hf ? p.eps1 : p.eps0) : 0.f;
 #pragma unroll
                         for (int rr = 0; rr < 8; ++rr) {
-                            const float t = __shfl_sync(FULL_MASK, tv[rr], LK - 1);
+                            const float t = __shfl_sync(FULL_MASK, tv[rr], LK - 1) - eps;
                             if (lane == 0) { s_tau[s * 8 + rr] = t; s_cnt[s * 8 + rr] = 0; }
                         }
                         if ((s & 3) == 0 && lane == 0) s_pool_cnt[cg] = 0;
@@ -471,8 +490,12 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// Per sub-key: out[r] = 1 / max(||key||, 1e-12) (or 1).  Optionally also, as a running maximum over the table,
+// eps = 2^-16 * ||key|| * out[r] * (1 + 2^-10) + 1e-6: how much a score can lose when the query's lo term is left
+// out of the contraction (|lo . key| <= ||lo|| ||key||, ||lo|| <= 2^-16 for a unit query half; the last terms
+// cover ||q|| = 1 up to rounding and the fp32 accumulation).
 __global__ void key_inv_norm_kernel(const __nv_bfloat16* __restrict__ keys, int n, int width, int do_norm,
-                                    float* __restrict__ out) {
+                                    float* __restrict__ out, float* __restrict__ eps) {
     const int lane = threadIdx.x & 31;
     const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (r >= n) return;
@@ -482,7 +505,14 @@ __global__ void key_inv_norm_kernel(const __nv_bfloat16* __restrict__ keys, int 
         ss = fmaf(v, v, ss);
     }
     ss = warp_sum(ss);
-    if (lane == 0) out[r] = do_norm ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
+    const float inv = do_norm ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
+    if (lane == 0) {
+        out[r] = inv;
+        if (eps) {
+            const float e = 1.52587890625e-5f * sqrtf(ss) * inv * 1.0009765625f + 1e-6f;
+            atomicMax(reinterpret_cast<int*>(eps), __float_as_int(e));  // positive floats order like their bit patterns
+        }
+    }
 }
 
 }  // namespace
@@ -507,9 +537,14 @@ cudaError_t select_tc_setup() {
                                 static_cast<int>(Smem::total));
 }
 
-cudaError_t launch_key_inv_norms(const void* keys, int n, int width, int do_norm, float* out, cudaStream_t s) {
+cudaError_t launch_key_inv_norms(const void* keys, int n, int width, int do_norm, float* out, cudaStream_t s,
+                                 float* eps) {
+    if (eps) {
+        const cudaError_t e = cudaMemsetAsync(eps, 0, sizeof(float), s);
+        if (e != cudaSuccess) return e;
+    }
     const unsigned blocks = static_cast<unsigned>((static_cast<int64_t>(n) * 32 + 255) / 256);
-    key_inv_norm_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(keys), n, width, do_norm, out);
+    key_inv_norm_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(keys), n, width, do_norm, out, eps);
     return cudaGetLastError();
 }
 
@@ -517,6 +552,7 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     if (a.rows == 0) return cudaSuccess;
     const int hw = a.Q / 2;
     CUtensorMap mq, mk0, mk1;
+    const int fast0 = a.eps0 && a.eps1;
     if (!make_tensor_map_bf16(&mq, a.q_split, static_cast<uint64_t>(3 * a.term_rows), static_cast<uint64_t>(a.Q),
                               static_cast<uint64_t>(a.Q), BM) ||
         !make_tensor_map_bf16(&mk0, a.keys0, static_cast<uint64_t>(a.n0), static_cast<uint64_t>(hw),
@@ -529,6 +565,7 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     p.n0 = a.n0; p.n1 = a.n1; p.kp0 = a.kp0; p.kp1 = a.kp1; p.k = a.k; p.mult0 = a.mult0; p.mult1 = a.mult1;
     p.ids32 = a.ids32; p.weights = a.weights; p.ids64 = a.ids64; p.raw_scores = a.raw_scores; p.prod_ids = a.prod_ids; p.status = a.status;
     p.overflow_rows = a.overflow_rows; p.overflow_count = a.overflow_count; p.stats = a.stats;
+    p.fast0 = fast0; p.eps0 = a.eps0; p.eps1 = a.eps1;
     const int64_t n_tiles = (a.rows + BM - 1) / BM;
     const unsigned grid = static_cast<unsigned>(n_tiles < a.sm_count ? n_tiles : a.sm_count);
     select_tc_kernel<<<grid, THREADS, Smem::total, s>>>(mq, mk0, mk1, p);
