@@ -200,24 +200,26 @@ int peer_gather_eval_partial(peer_handle_t h, const void* x, const int32_t* ids,
  * and softmax weights fp32, both [T, num_heads*top_k], into caller buffers - what this rank sends.
  * t->expert_down / expert_up / out are not read; t->ids_out / scores_out are filled when given.
  *
- * peer_route_tuples (sender): buckets the T*entries_per_token tuples by owner = id / rows_per_rank into
- * `send`, int32 [world, bucket_cap, 3] of (token_offset + token, id - owner*rows_per_rank, weight bits);
- * a bucket keeps (token, slot) order and is padded with token -1; ids outside [0, world*rows_per_rank)
- * are dropped.  bucket_cap >= T*entries_per_token always suffices.  world <= 64.
+ * peer_route_tuples (sender): sorts the T*E tuples of this rank's T tokens (E = entries_per_token) by owner =
+ * id / rows_per_rank into `send`: one block of int32 per destination rank, `world` blocks of
+ * 2*T*E + T words each, laid out [local row ids: T x E | weight bits: T x E | counts: T].  Row t holds,
+ * packed to the front in slot order, those of token t's tuples the destination owns (id - owner*rows_per_rank),
+ * counts[t] how many; unused slots are (row 0, weight 0); ids outside [0, world*rows_per_rank) go nowhere.
+ * One all-to-all of equal-size blocks then gives every rank `world` such blocks, and because a token's
+ * tuples only ever come from the rank that owns the token, block b row t IS the list of global token
+ * b*T + t: nothing is sorted or merged on the receiving side.  Deterministic; no handle; asynchronous.
  *
- * peer_pack_tuples (receiver): `recv`, int32 [world, bucket_cap, 3] as it arrives from the all-to-all,
- * becomes per-token lists ids_out int32 / weights_out fp32 [n_tokens, list_cap] and counts_out int32
- * [n_tokens] (entries beyond list_cap are dropped, unused slots are zero), in (source rank, position)
- * order: the input of peer_gather_eval_partial.
- *
- * Both routing kernels are deterministic (no atomics decide an order).  No handle; asynchronous. */
+ * peer_gather_eval_routed (receiver): peer_gather_eval_partial reading those received blocks in place:
+ * `recv` = int32 [world][2*T*E + T] as it arrives (T = tokens_per_rank, E = num_heads*top_k of the handle),
+ * x = the activations of all world*T tokens [world*T, input_dim], out_f32 [world*T, output_dim]. */
 int peer_select_tokens(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, int32_t* ids_out,
                        float* weights_out, void* stream);
 int peer_route_tuples(const int32_t* ids, const float* weights, int64_t n_tokens, int32_t entries_per_token,
-                      int32_t token_offset, int64_t rows_per_rank, int32_t world, int64_t bucket_cap,
-                      int32_t* send, void* stream);
-int peer_pack_tuples(const int32_t* recv, int32_t world, int64_t bucket_cap, int64_t n_tokens, int32_t list_cap,
-                     int32_t* ids_out, float* weights_out, int32_t* counts_out, void* stream);
+                      int64_t rows_per_rank, int32_t world, int32_t* send, void* stream);
+int peer_gather_eval_routed(peer_handle_t h, const void* x, const int32_t* recv, int32_t world,
+                            int64_t tokens_per_rank, const void* expert_down, const void* expert_up,
+                            const float* down_scale, const float* up_scale, int64_t n_local_rows,
+                            float* out_f32, void* stream);
 
 /* Backward of peer_gather_eval: the gradients autograd derives for the expert evaluation of the
  * reference (llm/models/experts.py:332-382; exercised by tests/test_peer_integration.py:181-192 and

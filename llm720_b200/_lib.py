@@ -49,10 +49,10 @@ EXPORTS = {
     "peer_select": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p,
                               C.c_void_p, C.c_void_p]),
     "peer_select_tokens": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p]),
-    "peer_route_tuples": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
-                                    C.c_int64, C.c_void_p, C.c_void_p]),
-    "peer_pack_tuples": (C.c_int, [C.c_void_p, C.c_int32, C.c_int64, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p,
-                                   C.c_void_p, C.c_void_p]),
+    "peer_route_tuples": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_void_p,
+                                    C.c_void_p]),
+    "peer_gather_eval_routed": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_select_stats": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_void_p]),
     "peer_select_nd": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p), C.c_int64, C.c_void_p, C.c_void_p,
                                  C.c_void_p]),

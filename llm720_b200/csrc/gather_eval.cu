@@ -167,6 +167,7 @@ struct GatherParams {
     float* out_f32;            // optional [T, Dout] fp32 output instead of `out`
     const void* residual;      // optional [T, Dout] in the activation dtype, added to the result
     int split;                 // the warps of a CTA share one token (few tokens: decode-shaped batches)
+    int64_t block_tokens, block_stride;   // ids / weights / counts laid out in per-rank blocks (see GatherArgs)
 };
 
 template <typename XT, typename TT, int CH, bool W10>
@@ -215,14 +216,18 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
     for (int64_t t = t_first; t < p.T && (alive || p.split); t += t_step) {
         // ---- token prologue: selections into shared memory, x into registers
         __syncwarp();
-        const int hk_token = p.counts ? min(max(p.counts[t], 0), p.HK) : p.HK;
+        // where this token's entries start: plain [T, HK] arrays, or the blocks an expert-parallel rank received
+        const int64_t tb = p.block_tokens ? t / p.block_tokens : 0;
+        const int64_t list0 = p.block_tokens ? tb * p.block_stride + (t - tb * p.block_tokens) * p.HK : t * p.HK;
+        const int64_t cnt_at = p.block_tokens ? tb * p.block_stride + (t - tb * p.block_tokens) : t;
+        const int hk_token = p.counts ? min(max(p.counts[cnt_at], 0), p.HK) : p.HK;
         // entries of this warp: all of the token's, or every WARPS-th one starting at `warp`
         const int e_first = p.split ? warp : 0, e_step = p.split ? WARPS : 1;
         const int hk = p.split ? (hk_token > warp ? (hk_token - warp + WARPS - 1) / WARPS : 0) : hk_token;
         const int total_rows = 2 * hk;
         for (int e = lane; e < hk; e += 32) {
-            int32_t id = p.ids[t * p.HK + e_first + e * e_step];
-            float w = p.weights[t * p.HK + e_first + e * e_step];
+            int32_t id = p.ids[list0 + e_first + e * e_step];
+            float w = p.weights[list0 + e_first + e * e_step];
             if (static_cast<uint32_t>(id) >= static_cast<uint64_t>(p.N)) {
                 atomicMax(p.status, STATUS_BOUNDS);
                 id = 0; w = 0.f;
@@ -497,6 +502,7 @@ cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
     p.N = a.N; p.D = a.D; p.Dout = a.Dout; p.activation = a.activation; p.status = a.status;
     p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
     p.counts = a.counts; p.out_f32 = a.out_f32; p.residual = a.residual; p.split = 0;
+    p.block_tokens = a.block_tokens; p.block_stride = a.block_stride;
     const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
     if (a.act_dtype == PEER_DTYPE_F32 && a.table_dtype == PEER_DTYPE_F32)
         return launch_ch<float, float>(a, p, max_ch, s);

@@ -119,6 +119,10 @@ struct GatherArgs {
     int rows_l2_resident;     // hint: the ids address so few rows that they stay in L2 (reference id arithmetic)
     const int32_t* counts;    // optional [T]: how many of token t's HK entries are in use
     float* out_f32;           // optional fp32 output [T, Dout] (partial sums of a row-sharded table)
+    // optional: ids / weights / counts are blocks as received from the ranks of an expert-parallel layer (route.cu):
+    // token t's entries start at ids[(t / block_tokens) * block_stride + (t % block_tokens) * HK] (same for weights),
+    // its count is counts[(t / block_tokens) * block_stride + t % block_tokens]; 0 = plain [T, HK] arrays
+    int64_t block_tokens, block_stride;
 };
 cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s);
 
@@ -187,13 +191,10 @@ struct SelectGradArgs {
 };
 cudaError_t launch_select_grad(const SelectGradArgs& a, cudaStream_t s);
 
-// Tuple routing of the expert-parallel layer (route.cu).  send: [world, bucket_cap, 3] int32 buckets of
-// (global token | -1, local row, weight bits); recv: the same shape as received from the peers.
+// Tuple routing of the expert-parallel layer (route.cu): `send` is [world] blocks of int32, each
+// [local row ids: T x E | weight bits: T x E | counts: T] for one destination rank.
 cudaError_t launch_route_tuples(const int32_t* ids, const float* weights, int64_t n_tokens, int entries_per_token,
-                                int token_offset, int64_t rows_per_rank, int world, int64_t bucket_cap, int32_t* send,
-                                cudaStream_t s);
-cudaError_t launch_pack_tuples(const int32_t* recv, int world, int64_t bucket_cap, int64_t n_tokens, int list_cap,
-                               int32_t* ids_out, float* weights_out, int32_t* counts_out, cudaStream_t s);
+                                int64_t rows_per_rank, int world, int32_t* send, cudaStream_t s);
 
 // LayerNorm over the model dimension, fp32 parameters (block_ln.cu)
 cudaError_t launch_block_ln(const void* x, int act_dtype, int64_t rows, int D, const float* w, const float* b, float eps,

@@ -377,7 +377,10 @@ static int select_tc_slice(peer_op* h, const void* keys0, const void* keys1, int
 // One slice (n <= max_tokens) of the layer, all pointers on the device.
 static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, void* out, int64_t* ids_out,
                          float* scores_out, int64_t n, cudaStream_t s, const void* residual = nullptr,
-                         int32_t* prod_out = nullptr) {
+                         int32_t* prod_out = nullptr, int32_t* sel_ids_to = nullptr, float* sel_w_to = nullptr) {
+    // where the selection goes: the handle's scratch, or (peer_select_tokens) the caller's buffers
+    int32_t* const sel_ids = sel_ids_to ? sel_ids_to : h->sel_ids;
+    float* const sel_w = sel_w_to ? sel_w_to : h->sel_w;
     const peer_config_t& c = h->cfg;
     QueryArgs q{};
     q.x = x; q.w = t->query_w; q.b = t->query_b; q.ln_w = t->ln_w; q.ln_b = t->ln_b;
@@ -410,7 +413,7 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         for (int d = 0; d < h->nd; ++d) { na.keys[d] = kk[d]; na.n[d] = h->n[d]; na.kp[d] = h->kp[d]; na.mult[d] = h->mult[d]; }
         na.nd = h->nd; na.Q = c.query_dim; na.k = c.top_k; na.norm_keys = c.norm_keys; na.norm_query = c.norm_query;
         na.act_dtype = c.act_dtype; na.rows = n * c.num_heads;
-        na.ids32 = h->sel_ids; na.weights = h->sel_w; na.ids64 = ids_out; na.raw_scores = scores_out;
+        na.ids32 = sel_ids; na.weights = sel_w; na.ids64 = ids_out; na.raw_scores = scores_out;
         na.prod_ids = prod_out;
         na.stride[h->nd - 1] = 1;
         for (int d = h->nd - 2; d >= 0; --d) na.stride[d] = na.stride[d + 1] * h->n[d + 1];
@@ -418,12 +421,12 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
         if (se == cudaErrorInvalidValue) return fail(h, PEER_ERR_UNSUPPORTED, "selection over this key grid is not implemented");
         CU_TRY(h, se);
     } else if (h->use_tc_select) {
-        const int rc_sel = select_tc_slice(h, t->keys0, t->keys1, n, h->sel_ids, h->sel_w, ids_out, scores_out, prod_out, s);
+        const int rc_sel = select_tc_slice(h, t->keys0, t->keys1, n, sel_ids, sel_w, ids_out, scores_out, prod_out, s);
         if (rc_sel) return rc_sel;
         h->launches += 1;
     } else {
         SelectArgs sa = select_args(h, n);
-        sa.ids32 = h->sel_ids; sa.weights = h->sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
+        sa.ids32 = sel_ids; sa.weights = sel_w; sa.ids64 = ids_out; sa.raw_scores = scores_out;
         sa.prod_ids = prod_out;
         CU_TRY(h, launch_select_simt(sa, s));
     }
@@ -435,7 +438,7 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     }
 
     GatherArgs g{};
-    g.x = x; g.ids = h->sel_ids; g.weights = h->sel_w; g.down = t->expert_down; g.up = t->expert_up;
+    g.x = x; g.ids = sel_ids; g.weights = sel_w; g.down = t->expert_down; g.up = t->expert_up;
     g.down_scale = t->down_scale; g.up_scale = t->up_scale; g.out = out; g.T = n;
     g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
@@ -722,44 +725,60 @@ extern "C" int peer_select_tokens(peer_handle_t h, const peer_tensors_t* t, int6
         const int64_t n = n_tokens - t0 < c.max_tokens ? n_tokens - t0 : c.max_tokens;
         rc = forward_slice(h, t, static_cast<const char*>(t->x) + t0 * c.input_dim * ab, nullptr,
                            t->ids_out ? t->ids_out + t0 * HK : nullptr, t->scores_out ? t->scores_out + t0 * HK : nullptr,
-                           n, s);
+                           n, s, nullptr, nullptr, ids_out + t0 * HK, weights_out + t0 * HK);
         if (rc) return rc;
-        CU_TRY(h, cudaMemcpyAsync(ids_out + t0 * HK, h->sel_ids, sizeof(int32_t) * n * HK, cudaMemcpyDeviceToDevice, s));
-        CU_TRY(h, cudaMemcpyAsync(weights_out + t0 * HK, h->sel_w, sizeof(float) * n * HK, cudaMemcpyDeviceToDevice, s));
     }
     return PEER_OK;
 }
 
 extern "C" int peer_route_tuples(const int32_t* ids, const float* weights, int64_t n_tokens, int32_t entries_per_token,
-                                 int32_t token_offset, int64_t rows_per_rank, int32_t world, int64_t bucket_cap,
-                                 int32_t* send, void* stream) {
+                                 int64_t rows_per_rank, int32_t world, int32_t* send, void* stream) {
     if (!ids || !weights || !send || n_tokens < 0) {
         peer::set_global_error("peer_route_tuples: null pointer or negative token count");
         return PEER_ERR_INVALID_ARG;
     }
-    const cudaError_t e = launch_route_tuples(ids, weights, n_tokens, entries_per_token, token_offset, rows_per_rank,
-                                              world, bucket_cap, send, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = launch_route_tuples(ids, weights, n_tokens, entries_per_token, rows_per_rank, world, send,
+                                              static_cast<cudaStream_t>(stream));
     if (e == cudaErrorInvalidValue) {
-        peer::set_global_error("peer_route_tuples: world must be 1..64, rows_per_rank, entries_per_token and bucket_cap positive");
+        peer::set_global_error("peer_route_tuples: world, rows_per_rank and entries_per_token must be positive");
         return PEER_ERR_INVALID_ARG;
     }
     if (e != cudaSuccess) { peer::set_global_error(cudaGetErrorString(e)); return PEER_ERR_CUDA; }
     return PEER_OK;
 }
 
-extern "C" int peer_pack_tuples(const int32_t* recv, int32_t world, int64_t bucket_cap, int64_t n_tokens, int32_t list_cap,
-                                int32_t* ids_out, float* weights_out, int32_t* counts_out, void* stream) {
-    if (!recv || !ids_out || !weights_out || !counts_out || n_tokens < 0) {
-        peer::set_global_error("peer_pack_tuples: null pointer or negative token count");
-        return PEER_ERR_INVALID_ARG;
-    }
-    const cudaError_t e = launch_pack_tuples(recv, world, bucket_cap, n_tokens, list_cap, ids_out, weights_out, counts_out,
-                                             static_cast<cudaStream_t>(stream));
-    if (e == cudaErrorInvalidValue) {
-        peer::set_global_error("peer_pack_tuples: world, bucket_cap and list_cap must be positive");
-        return PEER_ERR_INVALID_ARG;
-    }
-    if (e != cudaSuccess) { peer::set_global_error(cudaGetErrorString(e)); return PEER_ERR_CUDA; }
+extern "C" int peer_gather_eval_routed(peer_handle_t h, const void* x, const int32_t* recv, int32_t world,
+                                       int64_t tokens_per_rank, const void* expert_down, const void* expert_up,
+                                       const float* down_scale, const float* up_scale, int64_t n_local_rows,
+                                       float* out_f32, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    const peer_config_t& c = h->cfg;
+    if (!x || !recv || !expert_down || !expert_up || !out_f32)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_routed: null pointer");
+    if (world < 1 || tokens_per_rank < 0 || n_local_rows <= 0 || n_local_rows > c.num_experts)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_routed: world >= 1, tokens_per_rank >= 0, 0 < rows <= num_experts");
+    if (tokens_per_rank == 0) return PEER_OK;
+    if (h->hidden > 1 || c.act_dtype == PEER_DTYPE_F16)
+        return fail(h, PEER_ERR_UNSUPPORTED, "peer_gather_eval_routed: experts with several neurons and fp16 layers are not implemented");
+    if (c.table_dtype == PEER_DTYPE_E4M3 && (!down_scale || !up_scale))
+        return fail(h, PEER_ERR_INVALID_ARG, "FP8 tables need down_scale and up_scale");
+    if (!aligned16(x) || !aligned16(expert_down) || !aligned16(expert_up) || !aligned16(out_f32))
+        return fail(h, PEER_ERR_INVALID_ARG, "x, tables and out must be 16-byte aligned");
+    const int64_t E = static_cast<int64_t>(c.num_heads) * c.top_k;
+    GatherArgs g{};
+    g.x = x; g.ids = recv; g.weights = reinterpret_cast<const float*>(recv + tokens_per_rank * E);
+    g.counts = recv + 2 * tokens_per_rank * E;
+    g.block_tokens = tokens_per_rank; g.block_stride = 2 * tokens_per_rank * E + tokens_per_rank;
+    g.down = expert_down; g.up = expert_up; g.down_scale = down_scale; g.up_scale = up_scale;
+    g.out = out_f32; g.out_f32 = out_f32; g.T = tokens_per_rank * world; g.HK = static_cast<int>(E); g.N = n_local_rows;
+    g.D = c.input_dim; g.Dout = c.output_dim; g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype;
+    g.activation = c.activation; g.status = h->status; g.sm_count = h->sm_count;
+    cudaError_t e = launch_gather_eval(g, static_cast<cudaStream_t>(stream));
+    if (e == cudaErrorInvalidValue)
+        return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or %d entries per token, is not implemented",
+                    c.input_dim, c.output_dim, static_cast<int>(E));
+    CU_TRY(h, e);
+    h->launches += 1;
     return PEER_OK;
 }
 

@@ -292,6 +292,29 @@ class PeerOp:
                 _ptr(down_scale), _ptr(up_scale), down.shape[0], _ptr(out), T, _stream(self.device)))
         return out
 
+    def gather_eval_routed(self, x_all, recv, world: int, tokens_per_rank: int, down, up, down_scale=None,
+                           up_scale=None, out=None):
+        """Partial expert evaluation straight from the blocks an expert-parallel rank received (int32
+        [world, 2*T*E + T]: local row ids, weight bits, counts; see `sharded.route_tuples_blocks`): fp32 partial
+        sums [world*T, D_out] for all tokens against this rank's row shard."""
+        self._dev(x_all, "x", self.act_dtype)
+        self._dev(recv, "recv", torch.int32)
+        self._dev(down, "expert_down", self.table_dtype)
+        self._dev(up, "expert_up", self.table_dtype)
+        self._dev(down_scale, "down_scale", torch.float32)
+        self._dev(up_scale, "up_scale", torch.float32)
+        E = self.cfg.num_heads * self.cfg.top_k
+        if recv.shape != (world, 2 * tokens_per_rank * E + tokens_per_rank):
+            raise ValueError(f"recv is {tuple(recv.shape)}, expected {(world, 2 * tokens_per_rank * E + tokens_per_rank)}")
+        if out is None:
+            out = torch.empty(world * tokens_per_rank, self.cfg.output_dim, dtype=torch.float32, device=self.device)
+        self._dev(out, "out", torch.float32)
+        with torch.cuda.device(self.device):
+            self._check(self.lib.peer_gather_eval_routed(
+                self.handle, _ptr(x_all), _ptr(recv), int(world), int(tokens_per_rank), _ptr(down), _ptr(up),
+                _ptr(down_scale), _ptr(up_scale), down.shape[0], _ptr(out), _stream(self.device)))
+        return out
+
     def gather_eval_backward(self, x, grad_out, ids32, weights, down, up, grad_down=None, grad_up=None,
                              grad_dtype: torch.dtype = torch.float32):
         """Gradients of ``gather_eval``.  Returns (grad_x [T,D] fp32, grad_weights [T,H*k] fp32, grad_down

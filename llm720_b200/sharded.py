@@ -10,18 +10,20 @@ the layer for tables that do not fit, or should not be replicated, on every GPU:
 
   1. all-gather of the activations (every owner needs x_t for the tuples it will receive);
   2. each rank selects for ITS tokens (query projection + product-key retrieval kernels);
-  3. the selected (token, expert id, weight) tuples are bucketed by owner and exchanged with one
-     all-to-all (counts first, then the packed tuples);
+  3. the selected (token, expert id, weight) tuples are sorted by owner and exchanged with one
+     all-to-all of equal-size blocks (per destination: [local row ids T x E | weight bits T x E |
+     counts T], row t = those of token t's tuples the destination owns); a token's tuples only come
+     from the rank that owns the token, so the received blocks ARE the per-token lists;
   4. each rank evaluates the tuples it received against its row shard (one kernel, fp32 partial
      sums per token);
   5. reduce-scatter of the partial sums gives every rank the outputs of its own tokens.
 
 Result: identical to the single-device layer on the concatenated batch, up to fp32 summation
-order.  The exchange logic exists twice: as plain tensor code (`route_tuples*`, `pack_received*`)
-that runs on any device and is tested with CPU ranks over gloo, and as two kernels of the library
-(`peer_route_tuples`, `peer_pack_tuples`, wrapped by `route_tuples_native` / `pack_received_native`)
-that `ShardedPEER` uses on the GPU: one launch each instead of some twenty-five small tensor
-operations, same buckets and lists (a GPU test compares the two forms).
+order.  The exchange logic exists twice: as plain tensor code (`route_tuples_blocks`,
+`lists_from_blocks`, and the variable-length `route_tuples` / `pack_received`) that runs on any device
+and is tested with CPU ranks over gloo, and in the library (`peer_route_tuples`, one kernel, wrapped by
+`route_tuples_native`; `peer_gather_eval_routed`, the expert stage reading the received blocks in
+place) which `ShardedPEER` uses on the GPU; a GPU test compares the two forms.
 """
 from __future__ import annotations
 
@@ -86,30 +88,45 @@ def exchange(send: torch.Tensor, send_counts: torch.Tensor, group=None) -> torch
 
 
 # ---------------------------------------------------------------------------
-# Fixed-shape variant of the exchange: every rank sends every peer a bucket of the same capacity
-# (T_local*HK tuples, the worst case; 24 KB per peer at 8 tokens x 256 entries), unused slots carry
-# token -1.  One all-to-all, no counts to exchange, no host synchronisation, shapes that never change
-# from step to step.
+# Fixed-shape form of the exchange: every rank sends every peer one block of the same size,
+#     [ local row ids: T x E | weight bits: T x E | counts: T ]      (int32; T tokens of the sender, E = H*k)
+# row t holding, packed to the front in slot order, those of token t's tuples the peer owns.  One
+# all-to-all, no counts round, no host synchronisation, shapes that never change from step to step; and
+# since a token's tuples only come from the rank that owns it, block b row t of what arrives is already
+# the list of global token b*T + t.
 # ---------------------------------------------------------------------------
-def route_tuples_static(ids: torch.Tensor, weights: torch.Tensor, token_offset: int, rows: int, world: int) -> torch.Tensor:
-    """-> int32 [world, T*HK, 3] buckets of (global token | -1, local row, weight bits)."""
-    T, HK = ids.shape
-    n = T * HK
+def block_words(T: int, E: int) -> int:
+    return 2 * T * E + T
+
+
+def route_tuples_blocks(ids: torch.Tensor, weights: torch.Tensor, rows: int, world: int) -> torch.Tensor:
+    """ids [T, E] global expert ids, weights fp32 [T, E] -> int32 [world, 2*T*E + T]."""
+    T, E = ids.shape
     dev = ids.device
-    flat = ids.reshape(-1).to(torch.int64)
+    flat = ids.to(torch.int64)
     owner = torch.div(flat, rows, rounding_mode="floor")
-    order = torch.argsort(owner, stable=True)
-    owner_s = owner[order]
-    # fixed-size histogram (torch.bincount would read its bin count back to the host)
-    counts = torch.zeros(world, dtype=torch.int64, device=dev).scatter_add_(0, owner, torch.ones_like(owner))
-    start = torch.cumsum(counts, 0) - counts
-    pos = torch.arange(n, device=dev) - start[owner_s]
-    tok = (torch.arange(T, device=dev, dtype=torch.int64).repeat_interleave(HK) + token_offset)[order]
-    send = torch.full((world, n, 3), -1, dtype=torch.int32, device=dev)
-    send[owner_s, pos, 0] = tok.to(torch.int32)
-    send[owner_s, pos, 1] = (flat - owner * rows)[order].to(torch.int32)
-    send[owner_s, pos, 2] = weights.reshape(-1).to(torch.float32).view(torch.int32)[order]
+    wbits = weights.to(torch.float32).contiguous().view(torch.int32)
+    send = torch.zeros(world, block_words(T, E), dtype=torch.int32, device=dev)
+    trow = torch.arange(T, device=dev).unsqueeze(1).expand(T, E)
+    for r in range(world):
+        m = owner == r
+        pos = m.cumsum(1) - 1
+        b_ids = send[r, :T * E].view(T, E)
+        b_w = send[r, T * E:2 * T * E].view(T, E)
+        b_ids[trow[m], pos[m]] = (flat[m] - r * rows).to(torch.int32)
+        b_w[trow[m], pos[m]] = wbits[m]
+        send[r, 2 * T * E:] = m.sum(1).to(torch.int32)
     return send
+
+
+def lists_from_blocks(recv: torch.Tensor, T: int, E: int):
+    """Received blocks int32 [world, 2*T*E + T] -> (ids int32 [world*T, E], weights fp32 [world*T, E],
+    counts int32 [world*T]) of all tokens, global token b*T + t from block b row t."""
+    world = recv.shape[0]
+    ids = recv[:, :T * E].reshape(world * T, E)
+    w = recv[:, T * E:2 * T * E].contiguous().view(torch.float32).reshape(world * T, E)
+    cnt = recv[:, 2 * T * E:].reshape(world * T)
+    return ids.contiguous(), w, cnt.contiguous()
 
 
 def exchange_static(send: torch.Tensor, group=None) -> torch.Tensor:
@@ -118,66 +135,23 @@ def exchange_static(send: torch.Tensor, group=None) -> torch.Tensor:
     return recv
 
 
-def pack_received_static(recv: torch.Tensor, n_tokens: int, cap: int):
-    """Buckets int32 [world, m, 3] with -1 padding -> (ids int32 [T, cap], weights fp32 [T, cap],
-    counts int32 [T]); cap must be at least the longest per-token list (HK always is)."""
-    dev = recv.device
-    flat = recv.reshape(-1, 3)
-    tok = flat[:, 0].to(torch.int64)
-    key = torch.where(tok >= 0, tok, torch.full_like(tok, n_tokens))      # padding sorts behind every token
-    order = torch.argsort(key, stable=True)
-    key_s = key[order]
-    counts = torch.zeros(n_tokens + 1, dtype=torch.int64, device=dev).scatter_add_(0, key_s, torch.ones_like(key_s))
-    start = torch.cumsum(counts, 0) - counts
-    pos = torch.clamp(torch.arange(key_s.numel(), device=dev) - start[key_s], max=cap - 1)
-    ids = torch.zeros(n_tokens + 1, cap, dtype=torch.int32, device=dev)    # row T collects the padding
-    w = torch.zeros(n_tokens + 1, cap, dtype=torch.float32, device=dev)
-    ids[key_s, pos] = flat[order, 1]
-    w[key_s, pos] = flat[order, 2].contiguous().view(torch.float32)
-    return ids[:n_tokens], w[:n_tokens], torch.clamp(counts[:n_tokens], max=cap).to(torch.int32)
-
-
-def route_tuples_native(ids32: torch.Tensor, weights: torch.Tensor, token_offset: int, rows: int, world: int,
+def route_tuples_native(ids32: torch.Tensor, weights: torch.Tensor, rows: int, world: int,
                         send: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """`route_tuples_static` as one kernel (CUDA tensors): ids int32 [T, HK], weights fp32 [T, HK] ->
-    int32 [world, T*HK, 3]; a bucket keeps (token, slot) order, padding carries token -1."""
+    """`route_tuples_blocks` as one kernel of the library (CUDA tensors: int32 ids, fp32 weights)."""
     import ctypes as C
     from . import _lib
-    T, HK = ids32.shape
+    T, E = ids32.shape
     if ids32.dtype != torch.int32 or weights.dtype != torch.float32 or not ids32.is_cuda:
         raise TypeError("route_tuples_native takes CUDA tensors: int32 ids and fp32 weights")
     if send is None:
-        send = torch.empty(world, T * HK, 3, dtype=torch.int32, device=ids32.device)
+        send = torch.empty(world, block_words(T, E), dtype=torch.int32, device=ids32.device)
     lib = _lib.load()
     with torch.cuda.device(ids32.device):
         rc = lib.peer_route_tuples(C.c_void_p(ids32.contiguous().data_ptr()), C.c_void_p(weights.contiguous().data_ptr()),
-                                   T, HK, int(token_offset), int(rows), int(world), T * HK, C.c_void_p(send.data_ptr()),
+                                   T, E, int(rows), int(world), C.c_void_p(send.data_ptr()),
                                    C.c_void_p(torch.cuda.current_stream(ids32.device).cuda_stream))
     _lib.check(rc, None)
     return send
-
-
-def pack_received_native(recv: torch.Tensor, n_tokens: int, cap: int, out=None):
-    """`pack_received_static` as one kernel: buckets int32 [world, m, 3] -> (ids int32 [T, cap], weights fp32
-    [T, cap], counts int32 [T]), lists in (source rank, position) order."""
-    import ctypes as C
-    from . import _lib
-    if recv.dtype != torch.int32 or not recv.is_cuda or not recv.is_contiguous():
-        raise TypeError("pack_received_native takes a contiguous CUDA int32 tensor")
-    world, m, _ = recv.shape
-    dev = recv.device
-    if out is None:
-        out = (torch.empty(n_tokens, cap, dtype=torch.int32, device=dev),
-               torch.empty(n_tokens, cap, dtype=torch.float32, device=dev),
-               torch.empty(n_tokens, dtype=torch.int32, device=dev))
-    ids, w, cnt = out
-    lib = _lib.load()
-    with torch.cuda.device(dev):
-        rc = lib.peer_pack_tuples(C.c_void_p(recv.data_ptr()), int(world), int(m), int(n_tokens), int(cap),
-                                  C.c_void_p(ids.data_ptr()), C.c_void_p(w.data_ptr()), C.c_void_p(cnt.data_ptr()),
-                                  C.c_void_p(torch.cuda.current_stream(dev).cuda_stream))
-    _lib.check(rc, None)
-    return ids, w, cnt
 
 
 def reduce_scatter_rows(partial: torch.Tensor, group=None) -> torch.Tensor:
@@ -206,8 +180,8 @@ def sharded_forward(x_local: torch.Tensor, select_fn: Callable, eval_fn: Callabl
     dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=group)
     ids, w = select_fn(x_local)
     if static_shapes:
-        recv = exchange_static(route_tuples_static(ids, w, rank * t_local, rows, world), group)
-        p_ids, p_w, p_cnt = pack_received_static(recv, world * t_local, ids.shape[1])
+        recv = exchange_static(route_tuples_blocks(ids, w, rows, world), group)
+        p_ids, p_w, p_cnt = lists_from_blocks(recv, t_local, ids.shape[1])
     else:
         send, counts = route_tuples(ids, w, rank * t_local, rows, world)
         recv = exchange(send, counts, group)
@@ -266,21 +240,18 @@ class ShardedPEER:
             dev = x.device
             self._buf = dict(
                 x_all=torch.empty(world * T, D, dtype=x.dtype, device=dev),
-                send=torch.empty(world, T * HK, 3, dtype=torch.int32, device=dev),
-                recv=torch.empty(world, T * HK, 3, dtype=torch.int32, device=dev),
-                lists=(torch.empty(world * T, HK, dtype=torch.int32, device=dev),
-                       torch.empty(world * T, HK, dtype=torch.float32, device=dev),
-                       torch.empty(world * T, dtype=torch.int32, device=dev)))
+                send=torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev),
+                recv=torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev),
+                partial=torch.empty(world * T, L.output_dim, dtype=torch.float32, device=dev))
             self._buf_key = key
         b = self._buf
         dist.all_gather_into_tensor(b["x_all"], x, group=self.group)
         ids, wts = op.select_tokens(x, w)
-        route_tuples_native(ids, wts, rank * T, self.rows, world, b["send"])
+        route_tuples_native(ids, wts, self.rows, world, b["send"])
         dist.all_to_all_single(b["recv"], b["send"], group=self.group)
-        p_ids, p_w, p_cnt = pack_received_native(b["recv"], world * T, HK, b["lists"])
-        partial = op.gather_eval_partial(b["x_all"], p_ids, p_w, p_cnt, w["expert_down"], w["expert_up"],
-                                         w["down_scale"], w["up_scale"])
-        self.last_counts = p_cnt                  # tuples this rank evaluated, per token (device tensor)
+        partial = op.gather_eval_routed(b["x_all"], b["recv"], world, T, w["expert_down"], w["expert_up"],
+                                        w["down_scale"], w["up_scale"], b["partial"])
+        self.last_counts = b["recv"][:, 2 * T * HK:]     # tuples this rank evaluated, per token (device tensor)
         out = reduce_scatter_rows(partial, self.group)
         return out.to(hidden_states.dtype).view(B, S, -1)
 
@@ -291,8 +262,8 @@ class ShardedPEER:
         HK = L.num_heads * L.num_experts_per_tok
         eb = L.query_proj.weight.element_size()
         return {"all_gather_x": (G - 1) * T * L.input_dim * eb,
-                "all_to_all_buckets": (G - 1) * T * HK * 12,
-                "all_to_all_tuples_in_use": (G - 1) * T * HK * 12 // G,
+                "all_to_all_blocks": (G - 1) * block_words(T, HK) * 4,
+                "all_to_all_tuples_in_use": (G - 1) * T * HK * 8 // G,
                 "reduce_scatter_partials_fp32": (G - 1) * T * L.output_dim * 4}
 
     __call__ = forward

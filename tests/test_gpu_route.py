@@ -1,62 +1,73 @@
-"""The two routing kernels of the expert-parallel layer (peer_route_tuples, peer_pack_tuples) against the
-plain tensor form of the same logic (llm720_b200/sharded.py: route_tuples_static, pack_received_static),
-which the gloo CPU test checks against the oracle, and the query+selection stage entry that feeds them
-(peer_select_tokens) against the whole layer's selection.  Integer work: bit-exact."""
+"""The routing kernel of the expert-parallel layer (peer_route_tuples) against the plain tensor form of
+the same logic (llm720_b200/sharded.py: route_tuples_blocks), which the gloo CPU test checks against the
+variable-length routing and the oracle; the expert stage reading received blocks in place
+(peer_gather_eval_routed) against the list form (peer_gather_eval_partial); and the query+selection stage
+entry that feeds them (peer_select_tokens) against the whole layer's selection.  Integer work: bit-exact."""
 import pytest
 import torch
 
-from llm720_b200 import sharded, synthetic as syn
+from llm720_b200 import PeerOp, sharded, synthetic as syn
 from _util import make_op, op_weights
 
 pytestmark = pytest.mark.gpu
 
 
-def _as_sets(ids, w, cnt):
-    return [sorted(zip(ids[t, :int(cnt[t])].tolist(), w[t, :int(cnt[t])].tolist())) for t in range(ids.shape[0])]
-
-
-@pytest.mark.parametrize("T,HK,world,rows", [(8, 256, 8, 524288), (5, 6, 4, 8), (64, 256, 2, 2097152), (40, 48, 3, 100),
-                                              (1, 1, 1, 7)])
-def test_route_and_pack_kernels_equal_the_tensor_form(cuda_device, T, HK, world, rows):
-    g = torch.Generator().manual_seed(T * 1000 + HK)
-    ids = torch.randint(0, world * rows, (T, HK), generator=g)
+@pytest.mark.parametrize("T,E,world,rows", [(8, 256, 8, 524288), (5, 6, 4, 8), (64, 256, 2, 2097152), (40, 48, 3, 100),
+                                             (1, 1, 1, 7), (3, 33, 2, 50)])
+def test_route_kernel_equals_the_tensor_form(cuda_device, T, E, world, rows):
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    ids = torch.randint(0, world * rows, (T, E), generator=g)
     if T > 2:
         ids[2] = rows // 2                                  # one token sends everything to rank 0, duplicates included
-    w = torch.rand(T, HK, generator=g)
-    dev = cuda_device
-    ids_d, w_d = ids.to(torch.int32).to(dev), w.to(dev)
-    want = sharded.route_tuples_static(ids_d, w_d, 11, rows, world)
-    got = sharded.route_tuples_native(ids_d, w_d, 11, rows, world)
+    w = torch.rand(T, E, generator=g)
+    ids_d, w_d = ids.to(torch.int32).to(cuda_device), w.to(cuda_device)
+    want = sharded.route_tuples_blocks(ids_d, w_d, rows, world)
+    got = sharded.route_tuples_native(ids_d, w_d, rows, world)
     torch.cuda.synchronize()
-    assert got.shape == (world, T * HK, 3)
-    assert torch.equal(got[..., 0], want[..., 0])          # same stable order, same padding
-    used = got[..., 0] >= 0
-    assert torch.equal(got[used], want[used])
-    # receiving side: what arrives is [world, cap, 3] from the peers; reuse the buckets as if received
-    recv = got.clone()
-    recv[..., 0] = torch.where(recv[..., 0] >= 0, recv[..., 0] - 11, recv[..., 0])
-    a = sharded.pack_received_native(recv, T, HK)
-    b = sharded.pack_received_static(recv, T, HK)
-    torch.cuda.synchronize()
-    assert torch.equal(a[2], b[2])
-    assert _as_sets(a[0].cpu(), a[1].cpu(), a[2].cpu()) == _as_sets(b[0].cpu(), b[1].cpu(), b[2].cpu())
-    # every tuple arrives exactly once: global id = bucket * rows + local row
-    owner = torch.arange(world, device=dev).view(world, 1).expand(world, T * HK)
-    glob = (owner * rows + got[..., 1])[used]
-    have = sorted(zip((got[..., 0][used] - 11).tolist(), glob.tolist(), got[..., 2][used].view(torch.float32).tolist()))
-    exp = sorted(zip(torch.arange(T).repeat_interleave(HK).tolist(), ids.reshape(-1).tolist(), w.reshape(-1).tolist()))
-    assert have == exp
-    # a list shorter than the tuples of a token keeps the first ones and reports the capacity
-    c = sharded.pack_received_native(recv, T, max(HK // 2, 1))
-    assert int(c[2].max()) <= max(HK // 2, 1)
+    assert got.shape == (world, sharded.block_words(T, E))
+    assert torch.equal(got, want)                          # same slot order, same zero padding, same counts
+    assert int(got[:, 2 * T * E:].sum()) == T * E          # every tuple went to exactly one owner
 
 
 def test_route_drops_ids_outside_the_table(cuda_device):
     ids = torch.tensor([[0, 5, -1, 16, 3]], dtype=torch.int32, device=cuda_device)
     w = torch.ones(1, 5, device=cuda_device)
-    send = sharded.route_tuples_native(ids, w, 0, 8, 2)        # table of 16 rows on 2 ranks
-    assert int((send[..., 0] >= 0).sum()) == 3
-    assert send[0, :3, 1].tolist() == [0, 5, 3]
+    send = sharded.route_tuples_native(ids, w, 8, 2)          # table of 16 rows on 2 ranks
+    assert send[:, 10:].flatten().tolist() == [3, 0]
+    assert send[0, :3].tolist() == [0, 5, 3]
+
+
+@pytest.mark.parametrize("T,world", [(8, 8), (32, 2), (50, 4)])
+def test_routed_evaluation_equals_the_list_form(cuda_device, T, world):
+    """peer_gather_eval_routed reads the received blocks in place; peer_gather_eval_partial takes the same lists
+    as plain arrays.  Same kernel, same order of additions: bit-identical partial sums, in the split-token
+    form (few tokens) and the warp-per-token form."""
+    torch.manual_seed(T)
+    D, H, k, rows = 1024, 4, 8, 512
+    E = H * k
+    op = PeerOp(input_dim=D, output_dim=D, num_heads=H, query_dim=32, product_key_dim=(64, 64), top_k=k,
+                act_dtype=torch.bfloat16, table_dtype=torch.bfloat16, max_tokens=T * world, device=cuda_device)
+    U = (torch.randn(rows, D) * D ** -0.5).bfloat16().to(cuda_device)
+    V = (torch.randn(rows, D) * D ** -0.5).bfloat16().to(cuda_device)
+    x = torch.randn(T * world, D).bfloat16().to(cuda_device)
+    # what `world` peers would send this rank: each owns T tokens and this rank owns rows [0, rows) of world*rows
+    blocks = []
+    for b in range(world):
+        ids = torch.randint(0, world * rows, (T, E))
+        blocks.append(sharded.route_tuples_blocks(ids, torch.rand(T, E), rows, world)[0])
+    recv = torch.stack(blocks).to(cuda_device).contiguous()
+    got = op.gather_eval_routed(x, recv, world, T, U, V)
+    l_ids, l_w, l_cnt = sharded.lists_from_blocks(recv, T, E)
+    want = op.gather_eval_partial(x, l_ids, l_w.contiguous(), l_cnt, U, V)
+    op.query_status()
+    assert torch.equal(got, want)
+    ref = torch.zeros(T * world, D)
+    ic, wc, cc, xc, Uc, Vc = l_ids.cpu(), l_w.cpu(), l_cnt.cpu(), x.cpu().float(), U.cpu().float(), V.cpu().float()
+    for t in range(0, T * world, 7):
+        for j in range(int(cc[t])):
+            r = int(ic[t, j])
+            ref[t] += wc[t, j] * torch.nn.functional.gelu(Uc[r] @ xc[t]) * Vc[r]
+        assert torch.allclose(got[t].cpu(), ref[t], rtol=1e-4, atol=1e-5)
 
 
 def test_select_tokens_equals_the_layers_selection(cuda_device):

@@ -94,23 +94,32 @@ def test_route_and_pack_roundtrip():
     assert e_ids.shape == (3, 1) and int(e_cnt.sum()) == 0
 
 
-def test_static_route_and_pack_match_the_dynamic_ones():
+def test_block_routing_matches_the_variable_length_routing():
+    """The fixed-shape blocks ([local row ids | weight bits | counts] per destination) carry exactly the tuples
+    the variable-length routing sends, token by token and in slot order."""
     torch.manual_seed(1)
-    T, HK, world, rows = 6, 8, 4, 16
-    ids = torch.randint(0, world * rows, (T, HK))
+    T, E, world, rows = 6, 8, 4, 16
+    ids = torch.randint(0, world * rows, (T, E))
     ids[2] = 5                                      # one token sends everything to one owner
-    w = torch.rand(T, HK)
-    send = sharded.route_tuples_static(ids, w, 0, rows, world)
-    assert send.shape == (world, T * HK, 3)
+    w = torch.rand(T, E)
+    send = sharded.route_tuples_blocks(ids, w, rows, world)
+    assert send.shape == (world, sharded.block_words(T, E)) and send.dtype == torch.int32
+    dyn, counts = sharded.route_tuples(ids, w, 0, rows, world)
+    owner_of = torch.repeat_interleave(torch.arange(world), counts)
     for owner in range(world):
-        bucket = send[owner:owner + 1]
-        a_ids, a_w, a_cnt = sharded.pack_received_static(bucket, T, HK)
-        dyn = bucket[0][bucket[0, :, 0] >= 0]
-        b_ids, b_w, b_cnt = sharded.pack_received(dyn, T)
+        a_ids, a_w, a_cnt = sharded.lists_from_blocks(send[owner:owner + 1], T, E)
+        mine = dyn[owner_of == owner]
+        b_ids, b_w, b_cnt = sharded.pack_received(mine, T)
         assert torch.equal(a_cnt, b_cnt)
         for t in range(T):
             n = int(a_cnt[t])
-            assert sorted(zip(a_ids[t, :n].tolist(), a_w[t, :n].tolist())) == sorted(zip(b_ids[t, :n].tolist(), b_w[t, :n].tolist()))
+            assert a_ids[t, :n].tolist() == b_ids[t, :n].tolist()          # same order: slot order
+            assert a_w[t, :n].tolist() == b_w[t, :n].tolist()
+            assert a_ids[t, n:].abs().sum() == 0 and a_w[t, n:].abs().sum() == 0
+    # a received set of blocks is already the list of every token: block b, row t = global token b*T + t
+    recv = torch.stack([send[1], send[1]])
+    g_ids, g_w, g_cnt = sharded.lists_from_blocks(recv, T, E)
+    assert g_ids.shape == (2 * T, E) and torch.equal(g_cnt[:T], g_cnt[T:])
 
 
 def test_uneven_split_is_rejected():
