@@ -341,10 +341,10 @@ def run_e2e(env, layer, cfg, x, steps):
 
 
 def run_backward(env, layer, cfg, x, steps):
-    """Forward+backward of the layer (all parameters and x require gradients; table gradients summed in
-    fp32 and rounded once, the module's default), and the expert-stage gradient kernel on its own.
-    Algorithmic bytes of that kernel per (token, slot): the two table rows read, and the two fp32
-    gradient rows read and written."""
+    """Forward+backward of the layer (all parameters and x require gradients; table gradients summed as the
+    module's default policy decides, which is reported), and the expert-stage gradient kernel on its own
+    with fp32 and with bf16 sums.  Algorithmic bytes of that kernel per (token, slot): the two table rows
+    read, and the two gradient rows read and written."""
     T, HK = cfg.tokens, cfg.num_heads * cfg.top_k
     layer.requires_grad_(True)
     xg = x.clone().requires_grad_(True)
@@ -366,8 +366,11 @@ def run_backward(env, layer, cfg, x, steps):
     op = layer._op
     ids = layer._last_expert_indices.view(T, HK).to(torch.int32)
     w = torch.softmax(layer._last_expert_scores.view(T, cfg.num_heads, cfg.top_k), -1).view(T, HK).contiguous()
+    from llm720_b200.autograd import _table_grad_plan
+    gdt_used, rows_used = _table_grad_plan(layer, layer.expert_down.weight, T)
     out = {"fwd_bwd_ms_per_step": step_ms, "fwd_bwd_tokens_per_s": T / (step_ms / 1e3), "steps": steps,
-           "table_grad_sums": layer.table_grad_sums}
+           "table_grad_sums": f"{layer.table_grad_sums}: {str(gdt_used).replace('torch.', '')} sums over {rows_used} rows "
+                              f"({T * HK / rows_used:.1f} selections per row)"}
     peak, kind = hbm_peak()
     eb = torch.empty(0, dtype=cfg.table_dtype).element_size()
     x2, g2 = x.view(T, -1), grad_out.view(T, -1)

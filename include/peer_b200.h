@@ -238,6 +238,16 @@ int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_o
                               float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
                               int32_t grad_table_dtype, int64_t n_tokens, void* stream);
 
+/* The same with gradient tables of only n_grad_rows rows (grad_down [n_grad_rows, input_dim], grad_up
+ * [n_grad_rows, output_dim]) for callers who know that every id lies below n_grad_rows: with the reference's
+ * id arithmetic (i0 + i1, experts.py:203-230) ids stay below n_keys0 + n_keys1, so a few thousand rows of fp32
+ * sums (L2-resident) replace two dense fp32 tables.  An id at or beyond n_grad_rows is skipped and recorded in
+ * the status word like any id outside the table. */
+int peer_gather_eval_backward_rows(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
+                                   const float* weights, const void* expert_down, const void* expert_up,
+                                   float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
+                                   int32_t grad_table_dtype, int64_t n_grad_rows, int64_t n_tokens, void* stream);
+
 /* Backward of the score path: from grad_weights = dL/d(softmax weights) [T, num_heads, top_k] to
  * grad_queries = dL/d(queries after LayerNorm) [T, num_heads, query_dim] (fp32, written), through the
  * softmax, the selected scores and the per-slice query normalisation of experts.py:153-163, :327.

@@ -64,6 +64,7 @@ EXPORTS = {
     "peer_gather_eval_partial": (C.c_int, [C.c_void_p] * 5 + [C.c_int32] + [C.c_void_p] * 4 + [C.c_int64, C.c_void_p,
                                                                                            C.c_int64, C.c_void_p]),
     "peer_gather_eval_backward": (C.c_int, [C.c_void_p] * 11 + [C.c_int32, C.c_int64, C.c_void_p]),
+    "peer_gather_eval_backward_rows": (C.c_int, [C.c_void_p] * 11 + [C.c_int32, C.c_int64, C.c_int64, C.c_void_p]),
     "peer_usage_histogram": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_query_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "peer_launch_count": (C.c_int64, [C.c_void_p]),

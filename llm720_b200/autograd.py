@@ -19,11 +19,12 @@ dropout (training mode) the stages are separate nodes:
   per-slot factor, folded into the weights because each expert has one neuron);
 * expert evaluation: ``peer_gather_eval`` forward, ``peer_gather_eval_backward``
   backward (``_ExpertEval``): dense table gradients accumulated with vector
-  reductions in fp32 and rounded once to the parameters' dtype, which is what
-  the reference's embedding backward does for a bf16 layer (each row's sum is
-  formed in fp32).  ``module.table_grad_sums = "table"`` opts a bf16 layer into
-  sums formed in bf16 (half the traffic, one rounding per addend: only safe when
-  few tokens share a row).
+  reductions.  Rows that collect many contributions are summed in fp32 and
+  rounded once to the parameters' dtype, which is what the reference's embedding
+  backward does for a bf16 layer; where a batch brings only a few selections per
+  row, a bf16 layer may sum in bf16 (half the traffic, one rounding per addend).
+  ``module.table_grad_sums`` ("auto", "fp32", "table") decides; see
+  ``_table_grad_plan``.
 """
 from __future__ import annotations
 
@@ -57,32 +58,64 @@ class _ProjectQueries(torch.autograd.Function):
 
 class _ExpertEval(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weights, ids32, down, up, op, direct=False):
+    def forward(ctx, x, weights, ids32, down, up, op, plan=(torch.float32, None)):
         ctx.save_for_backward(x, weights, ids32, down, up)
         ctx.op = op
-        ctx.direct = direct
+        ctx.plan = plan
         return op.gather_eval(x, ids32, weights.contiguous(), down, up)
 
     @staticmethod
     def backward(ctx, grad_out):
         x, weights, ids32, down, up = ctx.saved_tensors
-        direct = ctx.direct
+        gdt, rows = ctx.plan
         gx, gw, gd, gu = ctx.op.gather_eval_backward(x, grad_out.contiguous(), ids32, weights.contiguous(), down, up,
-                                                     grad_dtype=down.dtype if direct else torch.float32)
+                                                     grad_dtype=gdt, grad_rows=rows)
         need = ctx.needs_input_grad
         return (gx.to(x.dtype) if need[0] else None, gw if need[1] else None, None,
-                gd.to(down.dtype) if need[3] else None, gu.to(up.dtype) if need[4] else None, None, None)
+                _dense_grad(gd, down) if need[3] else None, _dense_grad(gu, up) if need[4] else None, None, None)
 
 
-def _sums_in_table_dtype(module, table) -> bool:
-    """Whether the gradient kernel sums straight into a table of the parameters' 16-bit dtype.  Off unless the
-    module asks for it (``table_grad_sums = "table"``): a bf16 running sum loses small addends once a row
-    collects many contributions (with the reference's id arithmetic, ids < n0 + n1, a row of the 1 M-expert
-    layer takes about a thousand per batch).  Only single-neuron experts with rows of at most 4 KB have that
-    kernel form."""
-    return (getattr(module, "table_grad_sums", "fp32") == "table" and module.expert_hidden_size == 1 and
-            table.dtype == torch.bfloat16 and
-            max(module.input_dim, module.output_dim) * table.element_size() <= 4096)
+def _reachable_rows(module) -> int:
+    """Rows the layer's ids can address.  With the reference's id arithmetic the first key dimension never
+    gets its multiplier (experts.py:203-204), so ids stay below 1 + (n0 - 1) + sum_{d>0} (n_d - 1) * stride_d
+    (n0 + n1 - 1 for a two-dimensional grid); a one-dimensional grid returns candidate positions (< top_k)."""
+    dims = list(module.product_key_dim)
+    if module.index_mode != "reference":
+        return module.num_experts
+    if len(dims) == 1:
+        return min(module.num_experts, module.num_experts_per_tok)
+    strides = [1] * len(dims)
+    for d in range(len(dims) - 2, -1, -1):
+        strides[d] = strides[d + 1] * dims[d + 1]
+    return min(module.num_experts, 1 + (dims[0] - 1) + sum((dims[d] - 1) * strides[d] for d in range(1, len(dims))))
+
+
+def _table_grad_plan(module, table, n_tokens: int):
+    """(dtype of the sums, rows of the gradient tables).  bf16 sums exist for single-neuron experts of a bf16
+    layer with rows of at most 4 KB; a bf16 running sum loses small addends once a row collects many
+    contributions, so "auto" keeps them for batches with at most four selections per reachable row on average
+    and never with the reference's id arithmetic, where a few thousand rows take all of them (about a thousand
+    each at the 1 M-expert layer's batch).  With fp32 sums only the reachable rows get a buffer."""
+    mode = getattr(module, "table_grad_sums", "auto")
+    if mode not in ("auto", "fp32", "table"):
+        raise ValueError(f"table_grad_sums={mode!r}: 'auto', 'fp32' or 'table'")
+    reach = _reachable_rows(module)
+    eligible = (module.expert_hidden_size == 1 and table.dtype == torch.bfloat16 and
+                max(module.input_dim, module.output_dim) * table.element_size() <= 4096)
+    per_row = n_tokens * module.num_heads * module.num_experts_per_tok / max(reach, 1)
+    in_table = eligible and (mode == "table" or (mode == "auto" and module.index_mode != "reference" and per_row <= 4.0))
+    if in_table:
+        return table.dtype, module.num_experts            # summed straight into what becomes .grad
+    return torch.float32, reach
+
+
+def _dense_grad(compact: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    """Gradient of a whole table from sums over its first rows."""
+    if compact.shape[0] == like.shape[0]:
+        return compact.to(like.dtype)
+    g = torch.zeros(like.shape, dtype=like.dtype, device=like.device)
+    g[:compact.shape[0]] = compact
+    return g
 
 
 def _key_grid(module):
@@ -140,9 +173,9 @@ class _FusedLayer(torch.autograd.Function):
         H, Q, k = module.num_heads, module.query_dim, module.num_experts_per_tok
         need = ctx.needs_input_grad
         weights = torch.softmax(sc, dim=-1).view(T, H * k)
-        direct = _sums_in_table_dtype(module, down)
+        gdt, rows = _table_grad_plan(module, down, T)
         gx, gw, gd, gu = op.gather_eval_backward(x, grad_out.contiguous(), ids.view(T, H * k).to(torch.int32), weights,
-                                                 down, up, grad_dtype=down.dtype if direct else torch.float32)
+                                                 down, up, grad_dtype=gdt, grad_rows=rows)
         # score path: d(loss)/d(weights) = gw, pushed through softmax, the selected scores and the query path
         leaves = [None if t is None else t.detach().requires_grad_(n)
                   for t, n in zip((x, weight, bias, ln_w, ln_b), need[:5])]
@@ -159,7 +192,7 @@ class _FusedLayer(torch.autograd.Function):
         grads = [next(got) if (t is not None and t.requires_grad) else None for t in leaves]
         if need[0]:
             grads[0] = (gx + grads[0].float()).to(x.dtype)
-        return (*grads, gd.to(down.dtype) if need[5] else None, gu.to(up.dtype) if need[6] else None, None)
+        return (*grads, _dense_grad(gd, down) if need[5] else None, _dense_grad(gu, up) if need[6] else None, None)
 
 
 def peer_forward_autograd(module, hidden_states: torch.Tensor) -> torch.Tensor:
@@ -214,7 +247,7 @@ def _forward_with_dropout(module, x, w, B, S):
     weights = weights * F.dropout(torch.ones_like(weights), module.dropout.p, True)
     out = _ExpertEval.apply(x, weights.view(T, H * k), flat.to(torch.int32).view(T, H * k),
                             module.expert_down.weight, module.expert_up.weight, op,
-                            _sums_in_table_dtype(module, module.expert_down.weight))
+                            _table_grad_plan(module, module.expert_down.weight, T))
     if module.track_indices:
         module._stash(flat, scores.detach(), B, S)
     return out.view(B, S, module.output_dim)

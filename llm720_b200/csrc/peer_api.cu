@@ -907,12 +907,28 @@ extern "C" int peer_gather_eval_partial(peer_handle_t h, const void* x, const in
     return PEER_OK;
 }
 
+extern "C" int peer_gather_eval_backward_rows(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
+                                              const float* weights, const void* expert_down, const void* expert_up,
+                                              float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
+                                              int32_t grad_table_dtype, int64_t n_grad_rows, int64_t n_tokens, void* stream);
+
 extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
                                          const float* weights, const void* expert_down, const void* expert_up,
                                          float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
                                          int32_t grad_table_dtype, int64_t n_tokens, void* stream) {
     if (!h) return PEER_ERR_INVALID_ARG;
+    return peer_gather_eval_backward_rows(h, x, grad_out, ids, weights, expert_down, expert_up, grad_x, grad_weights,
+                                          grad_down, grad_up, grad_table_dtype, h->cfg.num_experts, n_tokens, stream);
+}
+
+extern "C" int peer_gather_eval_backward_rows(peer_handle_t h, const void* x, const void* grad_out, const int32_t* ids,
+                                              const float* weights, const void* expert_down, const void* expert_up,
+                                              float* grad_x, float* grad_weights, void* grad_down, void* grad_up,
+                                              int32_t grad_table_dtype, int64_t n_grad_rows, int64_t n_tokens, void* stream) {
+    if (!h) return PEER_ERR_INVALID_ARG;
     if (n_tokens == 0) return PEER_OK;
+    if (n_grad_rows <= 0 || n_grad_rows > h->cfg.num_experts)
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_backward_rows: n_grad_rows must lie in [1, num_experts]");
     const peer_config_t& c = h->cfg;
     if (!x || !grad_out || !ids || !weights || !expert_down || !expert_up || !grad_x || !grad_weights || !grad_down || !grad_up)
         return fail(h, PEER_ERR_INVALID_ARG, "peer_gather_eval_backward: null pointer");
@@ -926,7 +942,7 @@ extern "C" int peer_gather_eval_backward(peer_handle_t h, const void* x, const v
     GatherGradArgs g{};
     g.x = x; g.dy = grad_out; g.ids = ids; g.weights = weights; g.down = expert_down; g.up = expert_up;
     g.d_down = grad_down; g.d_up = grad_up; g.dx = grad_x; g.dweights = grad_weights;
-    g.T = n_tokens; g.HK = c.num_heads * c.top_k; g.N = c.num_experts; g.D = c.input_dim; g.Dout = c.output_dim;
+    g.T = n_tokens; g.HK = c.num_heads * c.top_k; g.N = n_grad_rows; g.D = c.input_dim; g.Dout = c.output_dim;
     g.act_dtype = c.act_dtype; g.table_dtype = c.table_dtype; g.activation = c.activation;
     g.status = h->status; g.sm_count = h->sm_count; g.hidden = h->hidden; g.grad_dtype = grad_table_dtype;
     // rows longer than 4 KB do not fit the register-resident kernel: the general kernel takes them (fp32 sums)

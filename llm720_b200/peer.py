@@ -316,10 +316,11 @@ class PeerOp:
         return out
 
     def gather_eval_backward(self, x, grad_out, ids32, weights, down, up, grad_down=None, grad_up=None,
-                             grad_dtype: torch.dtype = torch.float32):
+                             grad_dtype: torch.dtype = torch.float32, grad_rows: Optional[int] = None):
         """Gradients of ``gather_eval``.  Returns (grad_x [T,D] fp32, grad_weights [T,H*k] fp32, grad_down
         [N,D], grad_up [N,D_out]); the two table gradients are accumulated into the buffers passed in
-        (zero-initialised ones are made when none are given), in ``grad_dtype``: fp32, or the tables' bf16."""
+        (zero-initialised ones are made when none are given), in ``grad_dtype``: fp32, or the tables' bf16.
+        ``grad_rows``: the gradient tables cover rows [0, grad_rows) only (every id is known to lie below)."""
         if grad_dtype not in (torch.float32, self.table_dtype) or grad_dtype not in _DT:
             raise ValueError(f"table gradients are accumulated in fp32 or in the tables' dtype, not {grad_dtype}")
         self._dev(x, "x", self.act_dtype)
@@ -329,18 +330,21 @@ class PeerOp:
         self._dev(down, "expert_down", self.table_dtype)
         self._dev(up, "expert_up", self.table_dtype)
         T = x.shape[0]
+        n_rows = down.shape[0] if grad_rows is None else int(grad_rows)
         if grad_down is None:
-            grad_down = torch.zeros(down.shape, dtype=grad_dtype, device=self.device)
+            grad_down = torch.zeros(n_rows, down.shape[1], dtype=grad_dtype, device=self.device)
         if grad_up is None:
-            grad_up = torch.zeros(up.shape, dtype=grad_dtype, device=self.device)
+            grad_up = torch.zeros(n_rows, up.shape[1], dtype=grad_dtype, device=self.device)
         self._dev(grad_down, "grad_down", grad_dtype)
         self._dev(grad_up, "grad_up", grad_dtype)
+        if grad_down.shape[0] != n_rows or grad_up.shape[0] != n_rows:
+            raise ValueError(f"gradient tables must have {n_rows} rows")
         gx = torch.empty(T, self.cfg.input_dim, dtype=torch.float32, device=self.device)
         gw = torch.empty(T, self.cfg.num_heads * self.cfg.top_k, dtype=torch.float32, device=self.device)
         with torch.cuda.device(self.device):
-            self._check(self.lib.peer_gather_eval_backward(
+            self._check(self.lib.peer_gather_eval_backward_rows(
                 self.handle, _ptr(x), _ptr(grad_out), _ptr(ids32), _ptr(weights), _ptr(down), _ptr(up),
-                _ptr(gx), _ptr(gw), _ptr(grad_down), _ptr(grad_up), _DT[grad_dtype], T, _stream(self.device)))
+                _ptr(gx), _ptr(gw), _ptr(grad_down), _ptr(grad_up), _DT[grad_dtype], n_rows, T, _stream(self.device)))
         return gx, gw, grad_down, grad_up
 
     def query_status(self):
@@ -383,10 +387,13 @@ class PEER(nn.Module):
       ``_last_expert_scores`` (raw scores, fp32).
     * ``max_slice_tokens``: token capacity of the scratch; longer inputs run in
       slices.
-    * ``table_grad_sums``: ``"fp32"`` (default: the backward pass sums each table
-      row's gradient in fp32 and rounds once, like the reference's embedding
-      backward) or ``"table"`` (bf16 layers: sums formed in bf16, half the
-      traffic, for batches in which few tokens share a row).
+    * ``table_grad_sums``: how the backward pass sums a table row's gradient.
+      ``"fp32"``: in fp32, rounded once, like the reference's embedding backward.
+      ``"table"`` (bf16 layers): in bf16, half the traffic, one rounding per addend.
+      ``"auto"`` (default): fp32 whenever rows collect many contributions - always
+      with ``index_mode="reference"`` (ids stay below n0 + n1; then only those rows
+      get fp32 sums, not the whole table) and when a batch brings more than four
+      selections per table row on average - else ``"table"``.
     """
 
     def __init__(self, input_dim: int, output_dim: int, num_experts: int, num_experts_per_tok: int = 16,
@@ -434,7 +441,7 @@ class PEER(nn.Module):
         self.index_mode = "reference"
         self.track_indices = True
         self.max_slice_tokens = 16384
-        self.table_grad_sums = "fp32"
+        self.table_grad_sums = "auto"
         self._last_expert_indices: Optional[torch.Tensor] = None
         self._last_expert_scores: Optional[torch.Tensor] = None
         self._op: Optional[PeerOp] = None

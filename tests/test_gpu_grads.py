@@ -187,23 +187,31 @@ def test_bf16_layer_gradients_against_the_oracle(cuda_device, mode):
 
 def test_table_gradients_with_thousands_of_contributions_per_row(cuda_device):
     """The reference's id arithmetic (i0 + i1) sends every token to the same few rows: here 31 rows take
-    about four thousand contributions each.  The default backward sums them in fp32 and rounds once (what
-    the reference's embedding backward does), so the result stays at bf16 rounding of the fp32 sum; the
-    opt-in bf16 running sums are allowed to drift and only have to stay finite."""
+    about four thousand contributions each.  The default ("auto") backward sums such rows in fp32 - in a
+    buffer of just the reachable rows - and rounds once (what the reference's embedding backward does), so
+    the result stays at bf16 rounding of the fp32 sum; the opt-in bf16 running sums are allowed to drift and
+    only have to stay finite."""
     cfg = syn.PeerConfig("coll", 256, 256, 4, 64, (16, 16), 8, torch.bfloat16, torch.bfloat16, 4, 1024)
     sd = syn.make_weights(cfg, 21, "cpu", random_affine=True)
     x = syn.make_input(cfg, 21, "cpu")
     grad_out = torch.randn(cfg.batch, cfg.seq, cfg.output_dim, generator=torch.Generator().manual_seed(9)).to(cfg.dtype)
     ref = oracle_gradients(cfg, sd, x, grad_out.float(), "reference")
     m = _module(cfg, sd, cuda_device, "reference")
-    assert m.table_grad_sums == "fp32"
+    from llm720_b200.autograd import _table_grad_plan
+    assert m.table_grad_sums == "auto"
+    assert _table_grad_plan(m, m.expert_down.weight, cfg.tokens) == (torch.float32, 31)
+    m.index_mode = "product"
+    assert _table_grad_plan(m, m.expert_down.weight, 16) == (torch.bfloat16, 256)      # 2 selections per row
+    assert _table_grad_plan(m, m.expert_down.weight, cfg.tokens) == (torch.float32, 256)
+    m.index_mode = "reference"
     out, g = _module_grads(m, x.to(cuda_device), grad_out.to(cuda_device))
     m._op.query_status()
     per_row = torch.bincount(m._last_expert_indices.view(-1).cpu(), minlength=31)
     assert int(per_row.max()) > 2000 and int(m._last_expert_indices.max()) <= 30
     for k in GRAD_TABLES:
         a, b = g[k].float().cpu(), ref[k]
-        assert g[k].dtype == cfg.dtype
+        assert g[k].dtype == cfg.dtype and g[k].shape == (256, 256)
+        assert float(a[31:].abs().max()) == 0.0                       # rows the ids cannot reach
         l1 = float((a - b).abs().sum() / b.abs().sum())
         # fp32 atomics in another order + one bf16 rounding of each sum
         assert l1 <= 8e-3 and rel_err(a, b) <= 1e-2, (k, l1, rel_err(a, b))
