@@ -123,6 +123,19 @@ int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_tokens, voi
 int peer_block_forward(peer_handle_t h, const peer_tensors_t* t, const float* ln_w, const float* ln_b,
                        float ln_eps, int64_t n_tokens, void* stream);
 
+/* Tiered residency of the expert tables, for tables larger than the GPU's memory: the role of the reference's
+ * HierarchicalExpertCache (llm/models/kernels/peer_cutlass.cu:110-536; docs/MEMORY_HIERARCHY.md:5-11: HBM cache
+ * in front of pinned host memory), without its background thread and per-call table copies.  After this call
+ * the handle's forwards (peer_forward, peer_block_forward, peer_forward_host*) take t->expert_down / t->expert_up
+ * as the FULL tables in host memory that the GPU can address (pinned; with unified addressing the host pointer is
+ * the device pointer), and read a row from there only when row_map[id] < 0; a row with row_map[id] = s >= 0 is
+ * read from row s of cache_down / cache_up in HBM through the usual bulk-copy rings.  row_map: int32
+ * [num_experts] on the device; the caches: table_dtype, rows of input_dim / output_dim.  Per-row FP8 scales stay
+ * whole on the device.  The three arrays are the caller's and must stay valid; which rows to cache is the
+ * caller's policy (peer_usage_histogram gives the counts).  row_map = NULL switches back.  bf16 and FP8 tables
+ * of single-neuron experts; inference only. */
+int peer_set_row_tier(peer_handle_t h, const int32_t* row_map, const void* cache_down, const void* cache_up);
+
 /* Same, with t->x and t->out (and the optional ids/scores outputs) in HOST
  * memory (pinned for full speed): token slices are copied in, processed and
  * copied out on three internal streams so transfers overlap the kernels.

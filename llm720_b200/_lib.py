@@ -42,6 +42,7 @@ EXPORTS = {
     "peer_forward": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.c_void_p]),
     "peer_block_forward": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_void_p, C.c_void_p, C.c_float, C.c_int64,
                                      C.c_void_p]),
+    "peer_set_row_tier": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "peer_forward_host": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64]),
     "peer_forward_host_async": (C.c_int, [C.c_void_p, C.POINTER(PeerTensors), C.c_int64, C.POINTER(C.c_int64)]),
     "peer_forward_host_wait": (C.c_int, [C.c_void_p, C.c_int64]),

@@ -168,9 +168,12 @@ struct GatherParams {
     const void* residual;      // optional [T, Dout] in the activation dtype, added to the result
     int split;                 // the warps of a CTA share one token (few tokens: decode-shaped batches)
     int64_t block_tokens, block_stride;   // ids / weights / counts laid out in per-rank blocks (see GatherArgs)
+    // tiered residency (TIER instances only): row_map[id] >= 0 -> the row is slot row_map[id] of the HBM-resident
+    // cache_down / cache_up; < 0 -> it is read from `down` / `up`, which then point at host memory the GPU can address
+    const int32_t* row_map; const char* cache_down; const char* cache_up;
 };
 
-template <typename XT, typename TT, int CH, bool W10>
+template <typename XT, typename TT, int CH, bool W10, bool TIER>
 __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_eval_kernel(const GatherParams p) {
     using RC = RingCfg<TT, CH, W10>;
     constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
@@ -185,11 +188,12 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
     unsigned char* ring = smem + static_cast<size_t>(warp) * STAGES * SLOT;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(WARPS) * STAGES * SLOT) + warp * STAGES;
     unsigned char* lists = smem + static_cast<size_t>(WARPS) * STAGES * SLOT + WARPS * STAGES * 8;
-    const int per_warp_list = p.HK * (SCALED ? 16 : 8);
+    const int per_warp_list = p.HK * ((SCALED ? 16 : 8) + (TIER ? 4 : 0));
     int32_t* s_id = reinterpret_cast<int32_t*>(lists + static_cast<size_t>(warp) * per_warp_list);
     float* s_w = reinterpret_cast<float*>(s_id + p.HK);
     float* s_us = s_w + p.HK;       // only when SCALED
     float* s_vs = s_us + p.HK;
+    int32_t* s_slot = reinterpret_cast<int32_t*>(s_w + (SCALED ? 3 : 1) * p.HK);   // only when TIER: cache slot or -1
 
     const uint32_t ring_a = smem_u32(ring);
     const uint32_t bars_a = smem_u32(bars);
@@ -234,6 +238,7 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             }
             s_id[e] = id; s_w[e] = w;
             if (SCALED) { s_us[e] = __ldg(p.down_scale + id); s_vs[e] = __ldg(p.up_scale + id); }
+            if constexpr (TIER) s_slot[e] = __ldg(p.row_map + id);
         }
         // The activation row stays in registers for the whole token: fp32, or (rows longer than 64
         // elements per lane, bf16 activations) as packed bf16 pairs widened at each use.
@@ -296,6 +301,14 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             const char* src = is_v ? p.up + static_cast<int64_t>(id) * row_v
                                    : p.down + static_cast<int64_t>(id) * row_u;
             const uint32_t bytes = is_v ? row_v : row_u;
+            if constexpr (TIER) {
+                const int cs = s_slot[r >> 1];
+                if (cs < 0) {                 // host-resident row: nothing is staged, the consumer reads it in place;
+                    mbar_arrive(bars_a + 8 * s);   // the slot's phase completes at once so the ring keeps its order
+                    return;
+                }
+                src = is_v ? p.cache_up + static_cast<int64_t>(cs) * row_v : p.cache_down + static_cast<int64_t>(cs) * row_u;
+            }
             fence_proxy_async();
             mbar_expect_tx(bars_a + 8 * s, bytes);
             bulk_g2s(ring_a + s * SLOT, src, bytes, bars_a + 8 * s);
@@ -316,6 +329,9 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             float d0 = 0.f, d1 = 0.f;
             {
                 const unsigned char* rb = ring + slot * SLOT;
+                if constexpr (TIER) {         // a row that is not cached is read where it lives (host memory the GPU addresses)
+                    if (s_slot[e] < 0) rb = reinterpret_cast<const unsigned char*>(p.down) + static_cast<int64_t>(s_id[e]) * row_u;
+                }
 #pragma unroll
                 for (int i = 0; i < CH; ++i) {
                     const int c = lane + 32 * i;
@@ -357,6 +373,9 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
             if (!alive) break;
             {
                 const unsigned char* rb = ring + slot * SLOT;
+                if constexpr (TIER) {
+                    if (s_slot[e] < 0) rb = reinterpret_cast<const unsigned char*>(p.up) + static_cast<int64_t>(s_id[e]) * row_v;
+                }
 #pragma unroll
                 for (int i = 0; i < CH; ++i) {
                     const int c = lane + 32 * i;
@@ -428,17 +447,17 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
     }
 }
 
-template <typename XT, typename TT, int CH, bool W10>
+template <typename XT, typename TT, int CH, bool W10, bool TIER>
 size_t smem_bytes(int HK) {
     using RC = RingCfg<TT, CH, W10>;
     constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
     return static_cast<size_t>(WARPS) * RC::STAGES * RC::SLOT + WARPS * RC::STAGES * 8 +
-           static_cast<size_t>(WARPS) * HK * (sizeof(TT) == 1 ? 16 : 8);
+           static_cast<size_t>(WARPS) * HK * ((sizeof(TT) == 1 ? 16 : 8) + (TIER ? 4 : 0));
 }
 
-template <typename XT, typename TT, int CH, bool W10>
+template <typename XT, typename TT, int CH, bool W10, bool TIER = false>
 cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
-    const size_t smem = smem_bytes<XT, TT, CH, W10>(a.HK);
+    const size_t smem = smem_bytes<XT, TT, CH, W10, TIER>(a.HK);
     if (smem > MAX_SMEM) return cudaErrorInvalidValue;
     // Per instantiation and device; the attribute is sticky per function.  Setting it twice is harmless, so
     // two host threads (two handles) that meet here need only see a consistent flag: an atomic, no lock.
@@ -447,7 +466,7 @@ cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
     cudaError_t de = cudaGetDevice(&dev);
     if (de != cudaSuccess) return de;
     if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
-        cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH, W10>,
+        cudaError_t e = cudaFuncSetAttribute(gather_eval_kernel<XT, TT, CH, W10, TIER>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
@@ -463,12 +482,17 @@ cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
     q.split = a.counts != nullptr && a.T <= a.sm_count &&
               static_cast<size_t>(WARPS) * a.Dout * sizeof(float) <= static_cast<size_t>(WARPS) * RingCfg<TT, CH, W10>::STAGES * RingCfg<TT, CH, W10>::SLOT;
     if (q.split) ctas = a.T;
-    gather_eval_kernel<XT, TT, CH, W10><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(q);
+    gather_eval_kernel<XT, TT, CH, W10, TIER><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(q);
     return cudaGetLastError();
 }
 
 template <typename XT, typename TT, int CH>
 cudaError_t launch_t(const GatherArgs& a, const GatherParams& p, cudaStream_t s) {
+    if constexpr (sizeof(TT) <= 2) {          // tiered residency: 16-bit and FP8 tables
+        if (a.row_map) return launch_w<XT, TT, CH, false, true>(a, p, s);
+    } else {
+        if (a.row_map) return cudaErrorInvalidValue;
+    }
     if constexpr (sizeof(TT) == 2 && CH == 8) {
         if (a.rows_l2_resident) return launch_w<XT, TT, CH, true>(a, p, s);
     }
@@ -503,6 +527,7 @@ cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s) {
     p.nch_u = a.D * tb / 16; p.nch_v = a.Dout * tb / 16;
     p.counts = a.counts; p.out_f32 = a.out_f32; p.residual = a.residual; p.split = 0;
     p.block_tokens = a.block_tokens; p.block_stride = a.block_stride;
+    p.row_map = a.row_map; p.cache_down = static_cast<const char*>(a.cache_down); p.cache_up = static_cast<const char*>(a.cache_up);
     const int max_ch = p.nch_u > p.nch_v ? p.nch_u : p.nch_v;
     if (a.act_dtype == PEER_DTYPE_F32 && a.table_dtype == PEER_DTYPE_F32)
         return launch_ch<float, float>(a, p, max_ch, s);

@@ -123,6 +123,12 @@ struct GatherArgs {
     // token t's entries start at ids[(t / block_tokens) * block_stride + (t % block_tokens) * HK] (same for weights),
     // its count is counts[(t / block_tokens) * block_stride + t % block_tokens]; 0 = plain [T, HK] arrays
     int64_t block_tokens, block_stride;
+    // optional tiered residency: row_map [N] int32 on the device; row_map[id] >= 0: the row is that slot of
+    // cache_down / cache_up (HBM); < 0: it is read in place from down / up, which then point at host memory the GPU
+    // can address (pinned, unified addressing)
+    const int32_t* row_map;
+    const void* cache_down;
+    const void* cache_up;
 };
 cudaError_t launch_gather_eval(const GatherArgs& a, cudaStream_t s);
 

@@ -40,6 +40,10 @@ struct peer_op {
     int* ovf_count = nullptr;
     unsigned long long* sel_stats = nullptr;   // [2] accumulated: pooled row-halves, rows redone by the exact kernel
     float* sel_eps = nullptr;                  // [2] error bound of the select kernel's two-term first pass, per table
+    // tiered residency (peer_set_row_tier; caller-owned): which rows sit in the HBM cache, and the cache
+    const int32_t* tier_map = nullptr;
+    const void* tier_cache_down = nullptr;
+    const void* tier_cache_up = nullptr;
     void* x_ln = nullptr;         // [max_tokens, D] act dtype: LayerNorm of the block input (peer_block_forward)
     int32_t* sel_ids = nullptr;   // [max_tokens, H*k]
     float* sel_w = nullptr;       // [max_tokens, H*k]
@@ -448,6 +452,12 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
                          static_cast<int64_t>(c.n_keys0 + c.n_keys1) * (c.input_dim + c.output_dim) * act_bytes(c.table_dtype) <= (64LL << 20);
     const bool general_rows = h->hidden > 1 || c.act_dtype == PEER_DTYPE_F16;     // fp16 layers: the general kernel
     if (general_rows && g.hidden < 1) g.hidden = 1;
+    if (h->tier_map) {
+        if (general_rows || c.table_dtype == PEER_DTYPE_F32)
+            return fail(h, PEER_ERR_UNSUPPORTED, "tiered table residency: bf16 and FP8 tables of single-neuron experts only");
+        g.row_map = h->tier_map; g.cache_down = h->tier_cache_down; g.cache_up = h->tier_cache_up;
+        g.rows_l2_resident = 0;
+    }
     cudaError_t e = general_rows ? launch_gather_hidden(g, s) : launch_gather_eval(g, s);
     if (e == cudaErrorInvalidValue)
         return fail(h, PEER_ERR_UNSUPPORTED, "expert stage: row width %d/%d with this table dtype, or num_heads*top_k=%d, is not implemented",
@@ -455,6 +465,20 @@ static int forward_slice(peer_op* h, const peer_tensors_t* t, const void* x, voi
     CU_TRY(h, e);
     if (ev) CU_TRY(h, cudaEventRecord(ev[3], s));
     h->launches += 3;
+    return PEER_OK;
+}
+
+extern "C" int peer_set_row_tier(peer_handle_t h, const int32_t* row_map, const void* cache_down, const void* cache_up) {
+    if (!h) return PEER_ERR_INVALID_ARG;
+    if (!row_map) {             // back to tables that are wholly device-resident
+        h->tier_map = nullptr; h->tier_cache_down = nullptr; h->tier_cache_up = nullptr;
+        return PEER_OK;
+    }
+    if (!cache_down || !cache_up || !aligned16(cache_down) || !aligned16(cache_up))
+        return fail(h, PEER_ERR_INVALID_ARG, "peer_set_row_tier: both cache tables are required, 16-byte aligned");
+    if (h->hidden > 1 || h->cfg.act_dtype == PEER_DTYPE_F16 || h->cfg.table_dtype == PEER_DTYPE_F32)
+        return fail(h, PEER_ERR_UNSUPPORTED, "tiered table residency: bf16 and FP8 tables of single-neuron experts only");
+    h->tier_map = row_map; h->tier_cache_down = cache_down; h->tier_cache_up = cache_up;
     return PEER_OK;
 }
 

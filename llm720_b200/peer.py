@@ -71,6 +71,7 @@ class PeerOp:
         self.num_key_dims = len(product_key_dim)
         self.act_dtype, self.table_dtype = act_dtype, table_dtype
         self.handle = C.c_void_p()
+        self._tier = None
         with torch.cuda.device(self.device):
             rc = self.lib.peer_create(C.byref(cfg), C.byref(self.handle))
         if rc != _lib.OK:
@@ -110,7 +111,13 @@ class PeerOp:
         for k in ("query_w", "query_b", "ln_w", "ln_b", "keys0", "keys1", "keys2", "keys3"):
             self._dev(w.get(k), k, a)
         for k in ("expert_down", "expert_up"):
-            self._dev(w.get(k), k, tb)
+            tbl = w.get(k)
+            if self._tier is not None and tbl is not None and tbl.device.type == "cpu":
+                if not tbl.is_pinned():     # the kernels read uncached rows straight from this memory
+                    raise RuntimeError(f"{k} lives in host memory that is not pinned: the GPU cannot address it")
+                self._dev(tbl, k, tb, host_ok=True)
+            else:
+                self._dev(tbl, k, tb)
         for k in ("down_scale", "up_scale"):
             self._dev(w.get(k), k, torch.float32)
         return _lib.PeerTensors(
@@ -151,6 +158,25 @@ class PeerOp:
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_block_forward(self.handle, C.byref(t), _ptr(ln_w), _ptr(ln_b), float(eps),
                                                     hidden.shape[0], _stream(self.device)))
+
+    def set_row_tier(self, row_map: Optional[torch.Tensor], cache_down: Optional[torch.Tensor] = None,
+                     cache_up: Optional[torch.Tensor] = None):
+        """Tiered table residency (``peer_set_row_tier``): from now on ``expert_down`` / ``expert_up`` passed to the
+        forwards are the full tables in pinned host memory, ``row_map`` (int32 [num_experts], device) says which
+        rows are slots of the HBM-resident ``cache_down`` / ``cache_up``.  ``None`` switches back."""
+        if row_map is None:
+            self._check(self.lib.peer_set_row_tier(self.handle, None, None, None))
+            self._tier = None
+            return
+        self._dev(row_map, "row_map", torch.int32)
+        self._dev(cache_down, "cache_down", self.table_dtype)
+        self._dev(cache_up, "cache_up", self.table_dtype)
+        if row_map.numel() != self.cfg.num_experts:
+            raise ValueError(f"row_map has {row_map.numel()} entries for {self.cfg.num_experts} experts")
+        if int(row_map.max()) >= cache_down.shape[0] or cache_down.shape[0] != cache_up.shape[0]:
+            raise ValueError("row_map points past the end of the cache tables")
+        self._check(self.lib.peer_set_row_tier(self.handle, _ptr(row_map), _ptr(cache_down), _ptr(cache_up)))
+        self._tier = (row_map, cache_down, cache_up)          # kept alive with the handle
 
     def forward_host(self, x: torch.Tensor, w: dict, out: torch.Tensor, ids_out=None, scores_out=None):
         """x and out in (pinned) host memory; returns when out is complete."""
@@ -448,6 +474,7 @@ class PEER(nn.Module):
         self._op_key = None
         self._sel_op: Optional[PeerOp] = None
         self._sel_op_key = None
+        self._tier = None           # (row_map, cache_down, cache_up) while the tables live in host memory
 
     # -- FP8 tables ---------------------------------------------------------
     @torch.no_grad()
@@ -479,6 +506,52 @@ class PEER(nn.Module):
                 setattr(self, n + "_scale", torch.empty(scale.shape, dtype=scale.dtype, device=dev))
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
+    # -- tables larger than the GPU's memory -----------------------------------
+    @torch.no_grad()
+    def enable_host_tier(self, cache_rows: int, usage_counts: Optional[torch.Tensor] = None, device=None):
+        """Keep the expert tables in pinned host memory and only ``cache_rows`` rows of each in HBM: the role of
+        the reference's HierarchicalExpertCache (llm/models/kernels/peer_cutlass.cu:110-536,
+        docs/MEMORY_HIERARCHY.md:5-11).  The cached rows are the most used ones according to ``usage_counts``
+        (int64 [num_experts], e.g. ``DeviceUsageCounter`` totals; the first rows when none are given).  The
+        expert stage reads a cached row through its usual HBM rings and any other row in place from host memory
+        over PCIe.  Inference only; bf16 or FP8 tables, single-neuron experts.  Results are bit-identical to the
+        all-HBM layer.  Call again to re-pick the cached rows."""
+        if self.expert_hidden_size != 1 or self.expert_down.weight.dtype not in (torch.bfloat16, torch.float8_e4m3fn):
+            raise ValueError("host tiering: bf16 or FP8 tables of single-neuron experts")
+        dev = torch.device(device) if device is not None else self.query_proj.weight.device
+        if dev.type != "cuda":
+            raise RuntimeError("host tiering needs the small weights on a CUDA device")
+        N = self.num_experts
+        cache_rows = max(1, min(int(cache_rows), N))
+        if usage_counts is not None:
+            hot = torch.topk(usage_counts.to(dev).view(-1).float(), cache_rows).indices.sort().values
+        else:
+            hot = torch.arange(cache_rows, device=dev)
+        row_map = torch.full((N,), -1, dtype=torch.int32, device=dev)
+        row_map[hot] = torch.arange(cache_rows, dtype=torch.int32, device=dev)
+        caches = []
+        for name in ("expert_down", "expert_up"):
+            emb = getattr(self, name)
+            host = emb.weight.data
+            if host.device.type != "cpu" or not host.is_pinned():
+                host = host.cpu().pin_memory()
+            raw = host.view(torch.uint8) if host.element_size() == 1 else host      # row gather of FP8 payloads as bytes
+            caches.append(raw[hot.cpu()].view(host.dtype).to(dev).contiguous())
+            emb.weight = nn.Parameter(host, requires_grad=False)
+        self._tier = (row_map, caches[0], caches[1])
+        self._op = None                                  # the next forward builds a handle with the tier set
+        return self
+
+    def disable_host_tier(self, device=None):
+        """Move the tables back into device memory."""
+        dev = torch.device(device) if device is not None else self.query_proj.weight.device
+        for name in ("expert_down", "expert_up"):
+            emb = getattr(self, name)
+            emb.weight = nn.Parameter(emb.weight.data.to(dev), requires_grad=False)
+        self._tier = None
+        self._op = None
+        return self
+
     # -- operator management -------------------------------------------------
     def _weights(self) -> dict:
         ln = self.query_layer_norm
@@ -507,6 +580,8 @@ class PEER(nn.Module):
                               index_mode=self.index_mode, max_tokens=cap,
                               expert_hidden_size=self.expert_hidden_size, device=device)
             self._op_key = key
+            if self._tier is not None:
+                self._op.set_row_tier(*self._tier)
         return self._op
 
     def _product_operator(self, device, act_dtype, n_tokens: int) -> PeerOp:
@@ -528,8 +603,11 @@ class PEER(nn.Module):
         return self._sel_op
 
     def _needs_grad(self, hidden_states: torch.Tensor) -> bool:
-        return torch.is_grad_enabled() and (hidden_states.requires_grad or
+        need = torch.is_grad_enabled() and (hidden_states.requires_grad or
                                             any(p.requires_grad for p in self.parameters()))
+        if need and self._tier is not None:
+            raise RuntimeError("tables tiered into host memory are inference-only: call under torch.no_grad()")
+        return need
 
     def _prepare(self, hidden_states: torch.Tensor):
         if hidden_states.dim() != 3 or hidden_states.shape[-1] != self.input_dim:
