@@ -217,17 +217,20 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 if (norm_query) { n0 = fmaxf(sqrtf(s0), NORM_EPS); n1 = fmaxf(sqrtf(s1), NORM_EPS); }
             }
             if (q_hat_out || split_out) {
+                // one reciprocal per query half instead of a division per element (the quotient may differ from
+                // v / n in the last bit; scores move by about 1e-7, far inside the 1e-6 near-tie rule)
+                const float inv0 = 1.0f / n0, inv1 = 1.0f / n1;
                 for (int b = b_lo; b < b_hi; ++b) {
                     tc::tmem_ld32(taddr + b * 32, r);
                     tc::tmem_ld_wait();
-                    const float nn = (b * 32 < half) ? n0 : n1;
+                    const float inv_nn = (b * 32 < half) ? inv0 : inv1;
                     float y[32];
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int c = b * 32 + j;
                         float v = __uint_as_float(r[j]) + sb[c];
                         if (layer_norm) v = (v - mean) * rstd * s_gamma[c] + s_beta[c];
-                        y[j] = norm_query ? v / nn : v;
+                        y[j] = norm_query ? v * inv_nn : v;
                     }
                     if (grow < Ttok) {
                         if (q_hat_out) {
