@@ -103,8 +103,8 @@ int peer_create(const peer_config_t* cfg, peer_handle_t* out_handle);
 /* Replaces ~PEEROperatorEnhanced. */
 int peer_destroy(peer_handle_t h);
 
-/* Text of the last error on this handle (or of the last failed peer_create
- * when h is NULL).  Replaces the exceptions thrown at
+/* Text of the last error on this handle (or, when h is NULL, of the calling
+ * thread's last failed peer_create / handle-free call).  Replaces the exceptions thrown at
  * peer_cutlass_wrapper.cpp:90-96 and peer_cutlass.cu:1388-1394. */
 const char* peer_last_error(peer_handle_t h);
 

@@ -68,7 +68,8 @@ struct peer_op {
     std::string err;
 };
 
-static std::string g_create_error;
+// errors that have no handle to live on (failed peer_create, handle-free entry points): one text per host thread
+static thread_local std::string g_create_error;
 
 static int fail(peer_op* h, int code, const char* fmt, ...) {
     char buf[512];
