@@ -29,8 +29,12 @@ from __future__ import annotations
 
 from typing import Callable, Optional, Tuple
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
+
+from . import _lib
 
 
 def rows_per_rank(num_experts: int, world: int) -> int:
@@ -235,25 +239,43 @@ class ShardedPEER:
         w = L._weights()
         op = L._operator(x.device, x.dtype, T * world)
         HK = L.num_heads * L.num_experts_per_tok
-        key = (T, D, x.dtype, str(x.device))
+        key = (T, D, x.dtype, str(x.device), id(op)) + tuple(0 if v is None else v.data_ptr() for v in w.values())
         if self._buf_key != key:
-            dev = x.device
-            self._buf = dict(
-                x_all=torch.empty(world * T, D, dtype=x.dtype, device=dev),
-                send=torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev),
-                recv=torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev),
-                partial=torch.empty(world * T, L.output_dim, dtype=torch.float32, device=dev))
+            self._plan(op, w, T, D, x.dtype, x.device)
             self._buf_key = key
         b = self._buf
+        stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
         dist.all_gather_into_tensor(b["x_all"], x, group=self.group)
-        ids, wts = op.select_tokens(x, w)
-        route_tuples_native(ids, wts, self.rows, world, b["send"])
+        lib, h = op.lib, op.handle
+        # this rank's rows of x_all are x: the selection reads them there, so every pointer below is fixed
+        _lib.check(lib.peer_select_tokens(h, b["tensors_ref"], T, b["ids_p"], b["wts_p"], stream), h)
+        _lib.check(lib.peer_route_tuples(b["ids_p"], b["wts_p"], T, HK, self.rows, world, b["send_p"], stream), None)
         dist.all_to_all_single(b["recv"], b["send"], group=self.group)
-        partial = op.gather_eval_routed(b["x_all"], b["recv"], world, T, w["expert_down"], w["expert_up"],
-                                        w["down_scale"], w["up_scale"], b["partial"])
-        self.last_counts = b["recv"][:, 2 * T * HK:]     # tuples this rank evaluated, per token (device tensor)
-        out = reduce_scatter_rows(partial, self.group)
+        _lib.check(lib.peer_gather_eval_routed(h, b["x_all_p"], b["recv_p"], world, T, b["down_p"], b["up_p"], b["ds_p"],
+                                               b["us_p"], self.rows, b["partial_p"], stream), h)
+        self.last_counts = b["counts_view"]          # tuples this rank evaluated, per token (device tensor)
+        out = reduce_scatter_rows(b["partial"], self.group)
         return out.to(hidden_states.dtype).view(B, S, -1)
+
+    def _plan(self, op, w, T, D, dtype, dev):
+        """Buffers and pre-built C arguments of one step shape: a step is then three collectives and three library
+        calls with no allocation and no argument marshalling in between (the host's time to enqueue a step is what
+        bounds a decode-shaped batch)."""
+        L, world, rank = self.layer, self.world, dist.get_rank(self.group)
+        HK = L.num_heads * L.num_experts_per_tok
+        x_all = torch.empty(world * T, D, dtype=dtype, device=dev)
+        send = torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev)
+        recv = torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev)
+        partial = torch.empty(world * T, L.output_dim, dtype=torch.float32, device=dev)
+        ids = torch.empty(T, HK, dtype=torch.int32, device=dev)
+        wts = torch.empty(T, HK, dtype=torch.float32, device=dev)
+        x_mine = x_all[rank * T:(rank + 1) * T]
+        tensors = op._tensors(x_mine, w, None)
+        vp = lambda t: None if t is None else C.c_void_p(t.data_ptr())
+        self._buf = dict(x_all=x_all, send=send, recv=recv, partial=partial, ids=ids, wts=wts, tensors=tensors,
+                         tensors_ref=C.byref(tensors), ids_p=vp(ids), wts_p=vp(wts), send_p=vp(send), recv_p=vp(recv),
+                         x_all_p=vp(x_all), partial_p=vp(partial), down_p=vp(w["expert_down"]), up_p=vp(w["expert_up"]),
+                         ds_p=vp(w["down_scale"]), us_p=vp(w["up_scale"]), counts_view=recv[:, 2 * T * HK:])
 
     def nvlink_bytes_per_step(self, tokens_per_rank: int) -> dict:
         """Bytes each rank SENDS per step, by collective (fixed-shape buckets: the all-to-all carries
