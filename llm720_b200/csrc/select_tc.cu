@@ -89,6 +89,8 @@ constexpr int POOL = 64;           // candidates beyond CAP, per group of 32 row
 constexpr int LOST = 1 << 20;      // added to a row's count when one of its candidates could not be kept
 constexpr int STAGE_CAP = 8;       // scores a lane can hold back per chunk before they go to the row lists
 constexpr int GMAX_PITCH = 33;     // floats per key group in a row group's block of maxima (32 rows + 1: no bank conflicts)
+constexpr int CAND_PITCH = CAP + 1; // (score, sub-key) entries per row of the candidate lists: odd, so that the four-lanes-per-
+                                   // row loads of eight rows spread over the banks
 constexpr int THREADS = 128 + SCAN_WARPS * 32;
 constexpr int CTRL_REGS = 24, SCAN_REGS = 112;     // 128*24 + 512*112 <= 640*96 registers at launch
 constexpr uint32_t TMEM_COLS = 512;
@@ -103,7 +105,7 @@ struct Smem {
     // N_ACC accumulators apart, so one may be in pass 1 while another still reads its group maxima.
     static constexpr size_t gmax_off = k_off + static_cast<size_t>(K_STAGES) * K_STAGE_BYTES;
     static constexpr size_t cand_off = gmax_off + 4 * MAX_GROUPS * GMAX_PITCH * 4;               // [128][CAP] (key, col)
-    static constexpr size_t cnt_off = cand_off + BM * CAP * 8;                                   // [128] int
+    static constexpr size_t cnt_off = cand_off + BM * CAND_PITCH * 8;                            // [128] int
     static constexpr size_t tau_off = cnt_off + BM * 4;                                          // [128] int
     static constexpr size_t pool_off = tau_off + BM * 4;                                         // [POOL] (row, score, sub-key, -)
     static constexpr size_t bar_off = pool_off + 4 * POOL * 16;
@@ -128,6 +130,106 @@ struct SelTcParams {
 // order-preserving map fp32 -> int32 (and back): integer compares and redux.max work on scores
 __device__ __forceinline__ int f2key(float x) { const int i = __float_as_int(x); return i ^ ((i >> 31) & 0x7fffffff); }
 __device__ __forceinline__ float key2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
+
+// ---- bitonic networks over 32 elements held by FOUR ADJACENT LANES, eight per lane (element i = 8 * sub + e, sub =
+// lane & 3).  A warp sorts the lists of eight rows at once, each in its own group of four lanes; two thirds of the
+// compare-exchanges stay inside a lane, on registers, and only the strides 8 and 16 need a shuffle.  Result:
+// descending in i.  Direction of a compare-exchange at merge size K for element i: the lower index keeps the larger
+// value when (i & K) == 0 or K == 32.
+__device__ __forceinline__ void cx_val(float& a, float& b, bool a_gets_max) {
+    const float hi = fmaxf(a, b), lo = fminf(a, b);
+    a = a_gets_max ? hi : lo;
+    b = a_gets_max ? lo : hi;
+}
+// the same with a payload, ordered by (value descending, payload ascending): equal scores come out in the order of
+// their sub-key indices whatever slots the candidates arrived in, so a row's result does not depend on timing
+__device__ __forceinline__ void cx_pair(float& va, int& ca, float& vb, int& cb, bool a_gets_max) {
+    const bool a_first = (va > vb) || (va == vb && ca < cb);
+    const bool swap = a_first != a_gets_max;
+    const float tv = swap ? vb : va;
+    const int tc = swap ? cb : ca;
+    vb = swap ? va : vb; cb = swap ? ca : cb;
+    va = tv; ca = tc;
+}
+// strides 4, 2, 1 inside a lane
+__device__ __forceinline__ void g4_in_lane_val(float (&v)[8], int from_stride, bool a_gets_max) {
+#pragma unroll
+    for (int j = 4; j > 0; j >>= 1) {
+        if (j > from_stride) continue;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if ((e & j) == 0) cx_val(v[e], v[e | j], a_gets_max);
+    }
+}
+__device__ __forceinline__ void g4_in_lane_pair(float (&v)[8], int (&c)[8], int from_stride, bool a_gets_max) {
+#pragma unroll
+    for (int j = 4; j > 0; j >>= 1) {
+        if (j > from_stride) continue;
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+            if ((e & j) == 0) cx_pair(v[e], c[e], v[e | j], c[e | j], a_gets_max);
+    }
+}
+// merge sizes 2 and 4: the direction alternates inside a lane
+__device__ __forceinline__ void g4_first_stages_val(float (&v)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) cx_val(v[e], v[e + 1], (e & 2) == 0);                  // K = 2
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if ((e & 2) == 0) cx_val(v[e], v[e | 2], (e & 4) == 0);     // K = 4, stride 2
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) cx_val(v[e], v[e + 1], (e & 4) == 0);                  // K = 4, stride 1
+}
+__device__ __forceinline__ void g4_first_stages_pair(float (&v)[8], int (&c)[8]) {
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) cx_pair(v[e], c[e], v[e + 1], c[e + 1], (e & 2) == 0);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) if ((e & 2) == 0) cx_pair(v[e], c[e], v[e | 2], c[e | 2], (e & 4) == 0);
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) cx_pair(v[e], c[e], v[e + 1], c[e + 1], (e & 4) == 0);
+}
+// stride 8 or 16: the partner element lives in the lane `lane_xor` away; keep the larger when keep_max
+__device__ __forceinline__ void g4_cross_val(float (&v)[8], int lane_xor, bool keep_max) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float o = __shfl_xor_sync(FULL_MASK, v[e], lane_xor);
+        v[e] = keep_max ? fmaxf(v[e], o) : fminf(v[e], o);
+    }
+}
+__device__ __forceinline__ void g4_cross_pair(float (&v)[8], int (&c)[8], int lane_xor, bool keep_max) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float ov = __shfl_xor_sync(FULL_MASK, v[e], lane_xor);
+        const int oc = __shfl_xor_sync(FULL_MASK, c[e], lane_xor);
+        const bool mine_first = (v[e] > ov) || (v[e] == ov && c[e] < oc);
+        const bool take = mine_first != keep_max;
+        v[e] = take ? ov : v[e];
+        c[e] = take ? oc : c[e];
+    }
+}
+// the 16th largest of a row's 32 values: valid in the lanes with sub < 2
+__device__ __forceinline__ float g4_sixteenth_largest(float (&v)[8], int sub) {
+    const bool d8 = (sub & 1) == 0, d16 = (sub & 2) == 0;
+    g4_first_stages_val(v);
+    g4_in_lane_val(v, 4, d8);                                 // K = 8
+    g4_cross_val(v, 1, d8 == d16);                            // K = 16, stride 8
+    g4_in_lane_val(v, 4, d16);
+    g4_cross_val(v, 2, true);                                 // K = 32, stride 16: the lower half now holds the 16 largest
+    float m = v[0];
+#pragma unroll
+    for (int e = 1; e < 8; ++e) m = fminf(m, v[e]);
+    return fminf(m, __shfl_xor_sync(FULL_MASK, m, 1));
+}
+// full sort, descending in i = 8 * sub + e
+__device__ __forceinline__ void g4_sort_pairs(float (&v)[8], int (&c)[8], int sub) {
+    const bool d8 = (sub & 1) == 0, d16 = (sub & 2) == 0;
+    g4_first_stages_pair(v, c);
+    g4_in_lane_pair(v, c, 4, d8);                             // K = 8
+    g4_cross_pair(v, c, 1, d8 == d16);                        // K = 16
+    g4_in_lane_pair(v, c, 4, d16);
+    g4_cross_pair(v, c, 2, d16);                              // K = 32
+    g4_cross_pair(v, c, 1, d8);
+    g4_in_lane_pair(v, c, 4, true);
+}
 
 // candidate pairs of the final combine, two per lane: (a, b) with (a+1)(b+1) <= 16, row-major order
 __constant__ unsigned char c_pair_a[64];
@@ -312,7 +414,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                         const float x = slot[taken * 128];
                                         const int pos = atomicAdd(&s_cnt[row], 1);
                                         if (pos < CAP) {
-                                            s_cand[row * CAP + pos] = make_int2(__float_as_int(x), key);
+                                            s_cand[row * CAND_PITCH + pos] = make_int2(__float_as_int(x), key);
                                         } else {                             // a long list continues in the tile's pool
                                             const int pp = atomicAdd(s_pool_cnt + cg, 1);
                                             if (pp < POOL) s_pool[cg * POOL + pp] = make_int4(row, __float_as_int(x), key, 0);
@@ -337,36 +439,62 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
                     if (pass == 0) {
-                        // bound of my 8 rows: the 16th largest of the row's 32 group maxima (16 distinct scores reach it)
-                        // (the 8 rows' sorting networks are written side by side so their shuffles overlap)
+                        // bound of my 8 rows: the 16th largest of the row's 32 group maxima (16 distinct scores reach it).
+                        // Four lanes per row: lane 4*rr + sub holds the maxima of key groups 8*sub .. 8*sub+7 of row rr.
+                        const int rr = lane >> 2, sub = lane & 3;
                         float tv[8];
 #pragma unroll
-                        for (int rr = 0; rr < 8; ++rr) tv[rr] = s_gmax[(cg * MAX_GROUPS + lane) * GMAX_PITCH + quarter * 8 + rr];
-#pragma unroll
-                        for (int k = 2; k <= 32; k <<= 1)
-#pragma unroll
-                            for (int j = k >> 1; j > 0; j >>= 1) {
-                                const bool keep_max = ((lane & j) == 0) == ((lane & k) == 0 || k == 32);
-#pragma unroll
-                                for (int rr = 0; rr < 8; ++rr) {
-                                    const float o = __shfl_xor_sync(FULL_MASK, tv[rr], j);
-                                    tv[rr] = keep_max ? fmaxf(tv[rr], o) : fminf(tv[rr], o);
-                                }
-                            }
+                        for (int e = 0; e < 8; ++e) tv[e] = s_gmax[(cg * MAX_GROUPS + sub * 8 + e) * GMAX_PITCH + quarter * 8 + rr];
                         // fast form: the group maxima lack the lo term; the exact 16th best score is at least t - eps
                         const float eps = p.fast0 ? __ldg(hf ? p.eps1 : p.eps0) : 0.f;
-#pragma unroll
-                        for (int rr = 0; rr < 8; ++rr) {
-                            const float t = __shfl_sync(FULL_MASK, tv[rr], LK - 1) - eps;
-                            if (lane == 0) { s_tau[s * 8 + rr] = t; s_cnt[s * 8 + rr] = 0; }
-                        }
+                        const float t = g4_sixteenth_largest(tv, sub) - eps;
+                        if (sub == 0) { s_tau[s * 8 + rr] = t; s_cnt[s * 8 + rr] = 0; }
                         if ((s & 3) == 0 && lane == 0) s_pool_cnt[cg] = 0;
                         asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
                     }
                 }
                 // the 16 best candidates of my 8 rows, in order (score descending, sub-key ascending)
+                bool sorted_fast = false;
+                {
+                    // Common case, no list of these rows went on into the pool: four lanes per row sort the row's (at most
+                    // 32) candidates on registers; the sorted best 16 go back to the row's own list memory and are read
+                    // from there in the layout the final combine uses (rows 0-3 in lanes 0-15, rows 4-7 in lanes 16-31).
+                    const int rr = lane >> 2, sub = lane & 3;
+                    const int row = s * 8 + rr;
+                    const int cnt = s_cnt[row];
+                    const bool lost = cnt >= LOST;
+                    if (!__any_sync(FULL_MASK, !lost && cnt > CAP)) {
+                        const unsigned lm = __ballot_sync(FULL_MASK, lost);
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) overflow |= ((lm >> (4 * q)) & 1u) << q;
+                        float v[8]; int c[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            v[e] = -INFINITY; c[e] = INT_MAX;
+                            if (sub * 8 + e < min(cnt, CAP)) {
+                                const int2 en = s_cand[row * CAND_PITCH + sub * 8 + e];
+                                v[e] = __int_as_float(en.x); c[e] = en.y;
+                            }
+                        }
+                        g4_sort_pairs(v, c, sub);
+                        __syncwarp();                            // every lane of a row has read the list before it is rewritten
+                        if (sub < 2) {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) s_cand[row * CAND_PITCH + sub * 8 + e] = make_int2(__float_as_int(v[e]), c[e]);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int2 en = s_cand[(s * 8 + (half16 ? 4 : 0) + q) * CAND_PITCH + (lane & 15)];
+                            if (hf == 0) { hv[0][q] = __int_as_float(en.x); hc[0][q] = en.y; }
+                            else { hv[1][q] = __int_as_float(en.x); hc[1][q] = en.y; }
+                        }
+                        sorted_fast = true;
+                    }
+                }
+                // otherwise (a list of these rows continues in the pool: rare) one lane per candidate, four rows side by side
 #pragma unroll 1
-                for (int rb = 0; rb < 8; rb += 4) {          // four rows' networks side by side
+                for (int rb = 0; rb < 8 && !sorted_fast; rb += 4) {
                     float v[4]; int c[4];
                     unsigned pooled = 0;                     // bit q: the row's list continues in the pool
 #pragma unroll
@@ -379,7 +507,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             if (p.stats && lane == 0 && tile * BM + row < p.rows) atomicAdd(p.stats, 1ULL);
                         }
                         v[q] = -INFINITY; c[q] = INT_MAX;
-                        if (lane < min(cnt, CAP)) { const int2 e = s_cand[row * CAP + lane]; v[q] = __int_as_float(e.x); c[q] = e.y; }
+                        if (lane < min(cnt, CAP)) { const int2 e = s_cand[row * CAND_PITCH + lane]; v[q] = __int_as_float(e.x); c[q] = e.y; }
                     }
 #pragma unroll
                     for (int k = 2; k <= 32; k <<= 1)
