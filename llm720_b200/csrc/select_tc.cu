@@ -87,8 +87,11 @@ constexpr int LK = 16;             // list length per half (top_k and k' <= 16)
 constexpr int SCAN_WARPS = 16;
 constexpr int POOL = 64;           // candidates beyond CAP, per group of 32 rows (4 such pools per tile)
 constexpr int LOST = 1 << 20;      // added to a row's count when one of its candidates could not be kept
-constexpr int STAGE_CAP = 8;       // scores a lane can hold back per chunk before they go to the row lists
+constexpr int STAGE_CAP = 12;      // scores a lane can hold back per chunk before they go to the row lists: a sub-key that
+                                   // is a hit in more than this many of a lane's 32 rows sends the surplus rows to the
+                                   // exact kernel (with 12 a key in the top 16 of every fifth row still never does)
 constexpr int GMAX_PITCH = 33;     // floats per key group in a row group's block of maxima (32 rows + 1: no bank conflicts)
+constexpr int GROUP_BLOCK = STAGE_CAP * 128 > 32 * GMAX_PITCH ? STAGE_CAP * 128 : 32 * GMAX_PITCH;   // floats per row group
 constexpr int CAND_PITCH = CAP + 1; // (score, sub-key) entries per row of the candidate lists: odd, so that the four-lanes-per-
                                    // row loads of eight rows spread over the banks
 constexpr int THREADS = 128 + SCAN_WARPS * 32;
@@ -99,12 +102,12 @@ constexpr int KEY_MIN = INT_MIN;   // ordered-int image of "no score"
 struct Smem {
     static constexpr size_t q_off = 0;
     static constexpr size_t k_off = q_off + Q_BYTES;
-    // group maxima, one block per group of 32 rows (= per set of four scan warps): [4][MAX_GROUPS][GMAX_PITCH] float.
-    // The same block serves its four warps as staging slots in pass 1 ([STAGE_CAP][128] float), when their own
+    // group maxima, one block of GROUP_BLOCK floats per group of 32 rows (= per set of four scan warps):
+    // [MAX_GROUPS][GMAX_PITCH].  The same block serves its four warps as staging slots in pass 1 ([STAGE_CAP][128]), when their own
     // group maxima are dead.  Blocks of different row groups never overlap: the four sets of warps run up to
     // N_ACC accumulators apart, so one may be in pass 1 while another still reads its group maxima.
     static constexpr size_t gmax_off = k_off + static_cast<size_t>(K_STAGES) * K_STAGE_BYTES;
-    static constexpr size_t cand_off = gmax_off + 4 * MAX_GROUPS * GMAX_PITCH * 4;               // [128][CAP] (key, col)
+    static constexpr size_t cand_off = gmax_off + 4 * GROUP_BLOCK * 4;                           // [128][CAND_PITCH] (key, col)
     static constexpr size_t cnt_off = cand_off + BM * CAND_PITCH * 8;                            // [128] int
     static constexpr size_t tau_off = cnt_off + BM * 4;                                          // [128] int
     static constexpr size_t pool_off = tau_off + BM * 4;                                         // [POOL] (row, score, sub-key, -)
@@ -112,7 +115,7 @@ struct Smem {
     static constexpr size_t total = bar_off + 16 * sizeof(uint64_t) + 32 + 1008;
 };
 static_assert(Smem::total <= 227 * 1024, "shared memory budget");
-static_assert(STAGE_CAP * 128 <= MAX_GROUPS * GMAX_PITCH, "a row group's staging slots reuse its own group maxima");
+static_assert(STAGE_CAP * 128 <= GROUP_BLOCK && MAX_GROUPS * GMAX_PITCH <= GROUP_BLOCK, "a row group's staging slots reuse its own group maxima");
 
 struct SelTcParams {
     const float* invn0; const float* invn1;   // 1/||key|| per sub-key (or 1)
@@ -390,7 +393,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             // Every lane notes its own hits (score into a private slot, row into a bit
                             // mask) without votes or branches, then the lanes append their hits to the
                             // rows' lists side by side.
-                            float* slot = s_gmax + cg * (MAX_GROUPS * GMAX_PITCH) + quarter * 32 + lane;   // this row group's block
+                            float* slot = s_gmax + cg * GROUP_BLOCK + quarter * 32 + lane;   // this row group's block
                             constexpr uint32_t SLOT_STEP = 128 * 4;                      // bytes between a lane's slots
                             uint32_t addr = smem_u32(slot);
                             const uint32_t last = addr + (STAGE_CAP - 1) * SLOT_STEP;
@@ -434,7 +437,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         for (int j = 0; j < 32; ++j) {
                             float m = fmaxf(bnd[j], __shfl_xor_sync(FULL_MASK, bnd[j], 1));
                             m = fmaxf(m, __shfl_xor_sync(FULL_MASK, m, 2));
-                            if ((lane & 3) == 0) s_gmax[(cg * MAX_GROUPS + quarter * 8 + (lane >> 2)) * GMAX_PITCH + j] = m;
+                            if ((lane & 3) == 0) s_gmax[cg * GROUP_BLOCK + (quarter * 8 + (lane >> 2)) * GMAX_PITCH + j] = m;
                         }
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
@@ -444,7 +447,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         const int rr = lane >> 2, sub = lane & 3;
                         float tv[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) tv[e] = s_gmax[(cg * MAX_GROUPS + sub * 8 + e) * GMAX_PITCH + quarter * 8 + rr];
+                        for (int e = 0; e < 8; ++e) tv[e] = s_gmax[cg * GROUP_BLOCK + (sub * 8 + e) * GMAX_PITCH + quarter * 8 + rr];
                         // fast form: the group maxima lack the lo term; the exact 16th best score is at least t - eps
                         const float eps = p.fast0 ? __ldg(hf ? p.eps1 : p.eps0) : 0.f;
                         const float t = g4_sixteenth_largest(tv, sub) - eps;
