@@ -357,6 +357,52 @@ def test_fp8_tables(cuda_device):
     assert mx <= 5e-2 and l1 <= 8e-2, (mx, l1)
 
 
+def test_fp8_full_size_1m_experts(cuda_device):
+    """BASELINE configuration 3 at its full size: 1,048,576 experts with FP8-e4m3 tables (4.3 GB) and per-row
+    scales, the whole [8, 2048, 2048] batch; sampled tokens against the oracle on the dequantised rows (bf16
+    bound) and on the original bf16 rows (the looser bound of FP8 storage), and token-permutation equivariance
+    of the whole batch, bit for bit."""
+    cfg = syn.CONFIGS["c3"]
+    sd = syn.make_weights(cfg, 0, cuda_device)
+    x = syn.make_input(cfg, 0, cuda_device)
+    qd, sdn = syn.quantize_rows_e4m3(sd["expert_down.weight"])
+    qu, sup = syn.quantize_rows_e4m3(sd["expert_up.weight"])
+    sd8 = dict(sd); sd8["expert_down.weight"] = qd; sd8["expert_up.weight"] = qu
+    op, w, out, ids, sc = run_layer(cfg, sd8, x, cuda_device, "product", scales=(sdn, sup))
+    assert int(ids.max()) > 1_000_000 and int(ids.min()) >= 0
+    g = torch.Generator().manual_seed(1)
+    tok = torch.randperm(cfg.tokens, generator=g)[:64].sort().values
+    # oracle on the gathered rows only: the 8.6 GB of tables stay on the device
+    rows = ids[tok.to(cuda_device)].reshape(-1).unique()
+    remap = torch.full((cfg.num_experts,), -1, dtype=torch.int64, device=cuda_device)
+    remap[rows] = torch.arange(rows.numel(), device=cuda_device)
+    small = {k: v.cpu() for k, v in sd.items() if not k.startswith("expert_")}
+    def oracle_out(down_rows, up_rows, scales):
+        from oracle import peer_oracle as o
+        sel_ids = remap[ids[tok.to(cuda_device)]].cpu().unsqueeze(0)
+        wts = o.PeerWeights(None, None, None, None, [], down_rows, up_rows, *scales)
+        shape = o.PeerShape(cfg.input_dim, cfg.output_dim, rows.numel(), cfg.top_k, cfg.num_heads, 1, cfg.query_dim, [rows.numel(), 1])
+        with torch.no_grad():
+            return o.evaluate_experts(x.view(cfg.tokens, -1)[tok.to(cuda_device)].cpu().float().unsqueeze(0), sel_ids,
+                                      sc[tok.to(cuda_device)].cpu().unsqueeze(0), wts, shape).view(len(tok), -1)
+    # selection itself against the oracle (fp32 on the bf16 values of the small weights)
+    o_q = orc.make_queries(x.view(cfg.tokens, -1)[tok.to(cuda_device)].cpu().float().unsqueeze(0), oracle_weights(
+        {**small, "expert_down.weight": torch.zeros(1, 1), "expert_up.weight": torch.zeros(1, 1)}), oracle_shape(cfg))
+    o_ids, o_sc = orc.select(o_q, [small["sub_keys.0"].float(), small["sub_keys.1"].float()], cfg.top_k,
+                             cfg.product_key_dim, index_mode="product")
+    check_ids(ids[tok.to(cuda_device)], o_ids[0], o_sc[0], sc[tok.to(cuda_device)])
+    take8 = lambda t: t.view(torch.uint8)[rows].view(torch.float8_e4m3fn).cpu()      # FP8 payloads gathered as bytes
+    deq = oracle_out(take8(qd), take8(qu), (sdn[rows].cpu(), sup[rows].cpu()))
+    check_out(out[tok.to(cuda_device)], deq, cfg.dtype)
+    orig = oracle_out(sd["expert_down.weight"][rows].cpu().float(), sd["expert_up.weight"][rows].cpu().float(), (None, None))
+    mx, l1 = orc.output_errors(out[tok.to(cuda_device)].cpu().float(), orig)
+    assert mx <= 5e-2 and l1 <= 8e-2, (mx, l1)
+    perm = torch.randperm(cfg.tokens, generator=g).to(cuda_device)
+    outp = torch.empty_like(out)
+    op.forward(x.view(cfg.tokens, -1)[perm].contiguous(), w, outp)
+    assert torch.equal(outp, out[perm])
+
+
 @pytest.mark.parametrize("dtype_name", ["bf16", "fp8"])
 def test_decode_shaped_layer_d4096(cuda_device, dtype_name):
     """d_model 4096, 16 heads (256 row pairs per token), 64 single tokens: the long-row
