@@ -44,11 +44,14 @@
 //           hits to the rows' candidate lists (shared-memory atomicAdd for the
 //           position); a list longer than CAP continues in a small pool shared
 //           by 32 rows;
-//   then    per row, a bitonic sort of the candidates across the lanes of a
-//           warp (four rows' networks side by side), pool entries inserted
-//           afterwards; the 16 best stay, in order.
-// After both halves: candidate sums (a+1)(b+1) <= k, final top-k by repeated
-// redux.max / redux.min, softmax, ids; four rows per warp side by side.
+//   then    per row, a bitonic sort of the candidates by four adjacent lanes
+//           (eight rows' networks side by side in a warp; a list that went on
+//           into the pool takes a one-lane-per-candidate sort with the pool
+//           entries inserted afterwards); the 16 best stay, in order.
+// After both halves: the k best sums A[a] + B[b] of the two sorted lists, taken
+// one at a time as the largest head of the 16 sequences "a fixed, b ascending"
+// (four lanes per row hold four heads each; two shuffles per step), softmax,
+// ids; eight rows per warp side by side.
 // A row that loses a candidate (a lane with more than STAGE_CAP hits in one
 // chunk, or a full pool: heavily clustered scores) is written to a list that
 // the exact CUDA-core kernel reprocesses (select_simt.cu), so the result never
@@ -97,7 +100,6 @@ constexpr int CAND_PITCH = CAP + 1; // (score, sub-key) entries per row of the c
 constexpr int THREADS = 128 + SCAN_WARPS * 32;
 constexpr int CTRL_REGS = 24, SCAN_REGS = 112;     // 128*24 + 512*112 <= 640*96 registers at launch
 constexpr uint32_t TMEM_COLS = 512;
-constexpr int KEY_MIN = INT_MIN;   // ordered-int image of "no score"
 
 struct Smem {
     static constexpr size_t q_off = 0;
@@ -127,12 +129,9 @@ struct SelTcParams {
     int32_t* overflow_rows; int* overflow_count;   // rows left to the exact kernel
     unsigned long long* stats;                     // optional [2]: pooled row-halves, rows left to the exact kernel
     int fast0;                                     // pass 0 contracts two query terms instead of three
+    int vec_out;                                   // k == 16 and every output array 16-byte aligned: vector stores
     const float* eps0; const float* eps1;          // fast0: largest error of such a score, per table (device scalars)
 };
-
-// order-preserving map fp32 -> int32 (and back): integer compares and redux.max work on scores
-__device__ __forceinline__ int f2key(float x) { const int i = __float_as_int(x); return i ^ ((i >> 31) & 0x7fffffff); }
-__device__ __forceinline__ float key2f(int k) { return __int_as_float(k ^ ((k >> 31) & 0x7fffffff)); }
 
 // ---- bitonic networks over 32 elements held by FOUR ADJACENT LANES, eight per lane (element i = 8 * sub + e, sub =
 // lane & 3).  A warp sorts the lists of eight rows at once, each in its own group of four lanes; two thirds of the
@@ -233,10 +232,6 @@ __device__ __forceinline__ void g4_sort_pairs(float (&v)[8], int (&c)[8], int su
     g4_cross_pair(v, c, 1, d8);
     g4_in_lane_pair(v, c, 4, true);
 }
-
-// candidate pairs of the final combine, two per lane: (a, b) with (a+1)(b+1) <= 16, row-major order
-__constant__ unsigned char c_pair_a[64];
-__constant__ unsigned char c_pair_b[64];
 
 __global__ void __launch_bounds__(THREADS, 1)
 select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k0,
@@ -558,61 +553,105 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 }
             }
             if (!ok) continue;
-            // ---- candidate sums, final top-k, softmax, ids: one warp per row
-            const int pa0 = c_pair_a[lane], pb0 = c_pair_b[lane], pa1 = c_pair_a[lane + 32], pb1 = c_pair_b[lane + 32];
-            // only pairs with (a+1)(b+1) <= k can reach the top k: both lists are sorted
-            const bool use0 = pa0 < p.kp0 && pb0 < p.kp1 && (pa0 + 1) * (pb0 + 1) <= p.k;
-            const bool use1 = pa1 < p.kp0 && pb1 < p.kp1 && (pa1 + 1) * (pb1 + 1) <= p.k;
-#pragma unroll 1
-            for (int rb = 0; rb < 8; rb += 4) {              // four rows side by side
-                const int base = rb ? 16 : 0;                  // lane base + j: j-th best of each half
-                const int pos0 = pa0 * 16 + pb0, pos1 = pa1 * 16 + pb1;
-                int k0[4], k1[4], fk[4], fpos[4];
-                bool act[4];
+            // ---- the k best pair sums of each row, softmax, ids.  Both lists are sorted, so the sums A[a] + B[b] form one
+            // sequence per a that descends in b, and the best sum not yet taken is always the head of a sequence.  Four
+            // lanes per row (lane 4 * rr + sub keeps the heads of a = 4 * sub .. 4 * sub + 3), the warp's 8 rows at once:
+            // k steps of "largest head of the row, advance that sequence".  Equal sums go to the smaller a * 16 + b.
+            {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int64_t grow = tile * BM + s * 8 + rb + q;
-                    act[q] = grow < p.rows && !(overflow & (1u << (rb + q)));    // warp-uniform
-                    if (grow < p.rows && (overflow & (1u << (rb + q))) && lane == 0) { // left to the exact kernel
-                        p.overflow_rows[atomicAdd(p.overflow_count, 1)] = static_cast<int32_t>(grow);
-                        if (p.stats) atomicAdd(p.stats + 1, 1ULL);
-                    }
-                    const float s0 = hv[0][q], s1 = hv[1][q];
-                    const float v0 = __shfl_sync(FULL_MASK, s0, base + (pa0 & 15)) + __shfl_sync(FULL_MASK, s1, base + (pb0 & 15));
-                    const float v1 = __shfl_sync(FULL_MASK, s0, base + (pa1 & 15)) + __shfl_sync(FULL_MASK, s1, base + (pb1 & 15));
-                    k0[q] = use0 ? f2key(v0) : KEY_MIN; k1[q] = use1 ? f2key(v1) : KEY_MIN;
-                    fk[q] = KEY_MIN; fpos[q] = 0;
+                for (int q = 0; q < 4; ++q) {                  // the lists go to row memory: B at slots 0..15, A at 16..31
+                    int2* rowm = s_cand + (s * 8 + (half16 ? 4 : 0) + q) * CAND_PITCH;
+                    rowm[lane & 15] = make_int2(__float_as_int(hv[1][q]), hc[1][q]);
+                    rowm[16 + (lane & 15)] = make_int2(__float_as_int(hv[0][q]), hc[0][q]);
                 }
-                for (int it = 0; it < p.k; ++it) {
+                __syncwarp();
+                const int rr = lane >> 2, sub = lane & 3;
+                const int2* rowm = s_cand + (s * 8 + rr) * CAND_PITCH;
+                const int64_t grow = tile * BM + s * 8 + rr;
+                const bool lost_row = (overflow >> rr) & 1u;
+                if (grow < p.rows && lost_row && sub == 0) {   // left to the exact kernel
+                    p.overflow_rows[atomicAdd(p.overflow_count, 1)] = static_cast<int32_t>(grow);
+                    if (p.stats) atomicAdd(p.stats + 1, 1ULL);
+                }
+                float av[4], head[4];
+                int hpos[4];                                   // a * 16 + b of each head
+                const float b_first = __int_as_float(rowm[0].x);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int m = __reduce_max_sync(FULL_MASK, max(k0[q], k1[q]));
-                        const int mypos = min(k0[q] == m ? pos0 : INT_MAX, k1[q] == m ? pos1 : INT_MAX);
-                        const int pos = __reduce_min_sync(FULL_MASK, mypos);      // ties: smallest candidate position
-                        if (lane == it) { fk[q] = m; fpos[q] = pos; }
-                        if (k0[q] == m && pos0 == pos) k0[q] = KEY_MIN;
-                        else if (k1[q] == m && pos1 == pos) k1[q] = KEY_MIN;
-                    }
+                for (int i = 0; i < 4; ++i) {
+                    const int a = sub * 4 + i;
+                    av[i] = __int_as_float(rowm[16 + a].x);
+                    hpos[i] = a * 16;
+                    head[i] = a < p.kp0 ? av[i] + b_first : -INFINITY;
                 }
-                const bool live = lane < p.k;
+                float ov[4]; int op[4];                        // results it = 4 * sub .. 4 * sub + 3 of the row
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int i0 = __shfl_sync(FULL_MASK, hc[0][q], base + (live ? (fpos[q] >> 4) : 0));
-                    const int i1 = __shfl_sync(FULL_MASK, hc[1][q], base + (live ? (fpos[q] & 15) : 0));
-                    const int id = i0 * p.mult0 + i1 * p.mult1;
-                    const float fv = key2f(fk[q]);
-                    const float top = __shfl_sync(FULL_MASK, fv, 0);
-                    const float e = live ? expf(fv - top) : 0.f;
-                    const float w = e / warp_sum(e);
-                    if (live && act[q]) {
-                        const int64_t o = (tile * BM + s * 8 + rb + q) * p.k + lane;
-                        if (p.ids32) p.ids32[o] = id;
-                        if (p.weights) p.weights[o] = w;
-                        if (p.ids64) p.ids64[o] = id;
-                        if (p.raw_scores) p.raw_scores[o] = fv;
-                        if (p.prod_ids) p.prod_ids[o] = i0 * p.n1 + i1;
+                for (int j = 0; j < 4; ++j) { ov[j] = -INFINITY; op[j] = 0; }
+#pragma unroll
+                for (int it = 0; it < LK; ++it) {
+                    if (it < p.k) {                            // warp-uniform
+                        float bv = head[0]; int bp = hpos[0];
+#pragma unroll
+                        for (int i = 1; i < 4; ++i) {          // a ascends with i: strict compare keeps the smaller a
+                            const bool better = head[i] > bv;
+                            bv = better ? head[i] : bv; bp = better ? hpos[i] : bp;
+                        }
+#pragma unroll
+                        for (int m = 1; m <= 2; m <<= 1) {
+                            const float xv = __shfl_xor_sync(FULL_MASK, bv, m);
+                            const int xp = __shfl_xor_sync(FULL_MASK, bp, m);
+                            const bool other = (xv > bv) || (xv == bv && xp < bp);
+                            bv = other ? xv : bv; bp = other ? xp : bp;
+                        }
+                        if ((it >> 2) == sub) { ov[it & 3] = bv; op[it & 3] = bp; }
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            if ((bp >> 4) == sub * 4 + i) {    // my sequence was taken: its next element becomes the head
+                                const int nb = (bp & 15) + 1;
+                                if (nb < p.kp1) { hpos[i] = bp + 1; head[i] = av[i] + __int_as_float(rowm[nb].x); }
+                                else head[i] = -INFINITY;
+                            }
+                        }
                     }
                 }
+                const float top = __shfl_sync(FULL_MASK, ov[0], lane & ~3);
+                float e[4], sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { e[j] = sub * 4 + j < p.k ? expf(ov[j] - top) : 0.f; sum += e[j]; }
+                sum += __shfl_xor_sync(FULL_MASK, sum, 1);
+                sum += __shfl_xor_sync(FULL_MASK, sum, 2);
+                if (grow < p.rows && !lost_row) {
+                    int i0[4], i1[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) { i0[j] = rowm[16 + (op[j] >> 4)].y; i1[j] = rowm[op[j] & 15].y; }
+                    if (p.vec_out) {                           // k == 16, 16-byte aligned outputs: one store per array
+                        const int64_t o = grow * LK + sub * 4;
+                        const int4 id = make_int4(i0[0] * p.mult0 + i1[0] * p.mult1, i0[1] * p.mult0 + i1[1] * p.mult1,
+                                                  i0[2] * p.mult0 + i1[2] * p.mult1, i0[3] * p.mult0 + i1[3] * p.mult1);
+                        if (p.ids32) *reinterpret_cast<int4*>(p.ids32 + o) = id;
+                        if (p.weights) *reinterpret_cast<float4*>(p.weights + o) = make_float4(e[0] / sum, e[1] / sum, e[2] / sum, e[3] / sum);
+                        if (p.ids64) {
+                            *reinterpret_cast<longlong2*>(p.ids64 + o) = make_longlong2(id.x, id.y);
+                            *reinterpret_cast<longlong2*>(p.ids64 + o + 2) = make_longlong2(id.z, id.w);
+                        }
+                        if (p.raw_scores) *reinterpret_cast<float4*>(p.raw_scores + o) = make_float4(ov[0], ov[1], ov[2], ov[3]);
+                        if (p.prod_ids) *reinterpret_cast<int4*>(p.prod_ids + o) = make_int4(i0[0] * p.n1 + i1[0], i0[1] * p.n1 + i1[1],
+                                                                                             i0[2] * p.n1 + i1[2], i0[3] * p.n1 + i1[3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int it = sub * 4 + j;
+                            if (it >= p.k) continue;
+                            const int64_t o = grow * p.k + it;
+                            const int id = i0[j] * p.mult0 + i1[j] * p.mult1;
+                            if (p.ids32) p.ids32[o] = id;
+                            if (p.weights) p.weights[o] = e[j] / sum;
+                            if (p.ids64) p.ids64[o] = id;
+                            if (p.raw_scores) p.raw_scores[o] = ov[j];
+                            if (p.prod_ids) p.prod_ids[o] = i0[j] * p.n1 + i1[j];
+                        }
+                    }
+                }
+                __syncwarp();                                  // row memory is appended to again in the next tile
             }
         }
     }
@@ -655,15 +694,6 @@ bool select_tc_supported(int act_dtype, int Q, int n0, int n1, int k, int kp0, i
 }
 
 cudaError_t select_tc_setup() {
-    unsigned char pa[64], pb[64];
-    int np = 0;
-    for (int a = 0; a < LK; ++a)
-        for (int b = 0; b < LK; ++b)
-            if ((a + 1) * (b + 1) <= LK) { pa[np] = static_cast<unsigned char>(a); pb[np] = static_cast<unsigned char>(b); ++np; }
-    for (; np < 64; ++np) { pa[np] = 255; pb[np] = 255; }     // unused slots
-    cudaError_t e = cudaMemcpyToSymbol(c_pair_a, pa, sizeof pa);
-    if (e == cudaSuccess) e = cudaMemcpyToSymbol(c_pair_b, pb, sizeof pb);
-    if (e != cudaSuccess) return e;
     return cudaFuncSetAttribute(select_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 static_cast<int>(Smem::total));
 }
@@ -697,6 +727,10 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     p.ids32 = a.ids32; p.weights = a.weights; p.ids64 = a.ids64; p.raw_scores = a.raw_scores; p.prod_ids = a.prod_ids; p.status = a.status;
     p.overflow_rows = a.overflow_rows; p.overflow_count = a.overflow_count; p.stats = a.stats;
     p.fast0 = fast0; p.eps0 = a.eps0; p.eps1 = a.eps1;
+    const uintptr_t out_bits = reinterpret_cast<uintptr_t>(a.ids32) | reinterpret_cast<uintptr_t>(a.weights) |
+                               reinterpret_cast<uintptr_t>(a.ids64) | reinterpret_cast<uintptr_t>(a.raw_scores) |
+                               reinterpret_cast<uintptr_t>(a.prod_ids);
+    p.vec_out = a.k == LK && (out_bits & 15u) == 0;
     const int64_t n_tiles = (a.rows + BM - 1) / BM;
     const unsigned grid = static_cast<unsigned>(n_tiles < a.sm_count ? n_tiles : a.sm_count);
     select_tc_kernel<<<grid, THREADS, Smem::total, s>>>(mq, mk0, mk1, p);
