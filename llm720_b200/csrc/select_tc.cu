@@ -427,12 +427,21 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         }
                     }
                     if (pass == 0) {
-                        // group maxima: 4 adjacent lanes x all chunks = one group; 8 groups per warp, 32 per row
+                        // group maxima: 4 adjacent lanes x all chunks = one group; 8 groups per warp, 32 per row.
+                        // Each exchange halves what a lane keeps (the partner gets the other half), so the four
+                        // lanes end with 8 rows' maxima each: 24 shuffles instead of 64.
+                        const bool up1 = lane & 1, up2 = lane & 2;
+                        float h1[16];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            float m = fmaxf(bnd[j], __shfl_xor_sync(FULL_MASK, bnd[j], 1));
-                            m = fmaxf(m, __shfl_xor_sync(FULL_MASK, m, 2));
-                            if ((lane & 3) == 0) s_gmax[cg * GROUP_BLOCK + (quarter * 8 + (lane >> 2)) * GMAX_PITCH + j] = m;
+                        for (int i = 0; i < 16; ++i) {                   // h1[i]: row i + 16 * up1
+                            const float got = __shfl_xor_sync(FULL_MASK, up1 ? bnd[i] : bnd[i + 16], 1);
+                            h1[i] = fmaxf(up1 ? bnd[i + 16] : bnd[i], got);
+                        }
+                        float* gm = s_gmax + cg * GROUP_BLOCK + (quarter * 8 + (lane >> 2)) * GMAX_PITCH + (up1 ? 16 : 0) + (up2 ? 8 : 0);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {                    // row i + 8 * up2 + 16 * up1
+                            const float got = __shfl_xor_sync(FULL_MASK, up2 ? h1[i] : h1[i + 8], 2);
+                            gm[i] = fmaxf(up2 ? h1[i + 8] : h1[i], got);
                         }
                     }
                     asm volatile("bar.sync %0, 128;" ::"r"(1 + cg) : "memory");      // the four warps that share these 32 rows
