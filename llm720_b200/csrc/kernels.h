@@ -53,16 +53,17 @@ struct SelectTcArgs {
     unsigned long long* stats;     // optional [2], accumulated: row-halves whose candidate list continued in the
                                    // pool; rows handed to the exact kernel
     // optional (both or none; only for layers that normalise their queries): the first pass leaves out the
-    // query's lo term.  eps0/1: device scalars, the most a score can lose by that (from launch_key_inv_norms)
+    // query's lo term.  eps0/1: device scalars, the most a score can lose by that (from launch_key_prep)
     const float* eps0; const float* eps1;
 };
 bool select_tc_supported(int act_dtype, int Q, int n0, int n1, int k, int kp0, int kp1);
 cudaError_t select_tc_setup();
 cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s);
-// out[j] = 1 / max(||keys[j]||, 1e-12), or 1 when !do_norm (bf16 keys); with eps also the error bound of the
-// select kernel's two-term first pass (a device scalar, zeroed first)
-cudaError_t launch_key_inv_norms(const void* keys, int n, int width, int do_norm, float* out, cudaStream_t s,
-                                 float* eps = nullptr);
+// Both bf16 sub-key tables in one launch: invn[j] = 1 / max(||key_j||, 1e-12) (or 1 when !do_norm), khat = the
+// normalised keys in fp32, transposed [width, n] (what launch_normalize_rows writes with transpose_out), and with
+// eps (a device pair, zeroed here) the error bounds of the select kernel's two-term first pass, one per table
+cudaError_t launch_key_prep(const void* keys0, const void* keys1, int n0, int n1, int width, int do_norm, float* khat0,
+                            float* khat1, float* invn0, float* invn1, float* eps, cudaStream_t s);
 
 // rows of `width` elements -> fp32, each row divided by max(||row||, 1e-12) when do_norm;
 // written [rows, width], or [width, rows] when transpose_out

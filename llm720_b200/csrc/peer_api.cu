@@ -334,13 +334,13 @@ static int normalise_keys(peer_op* h, const void* keys0, const void* keys1, cuda
     return PEER_OK;
 }
 
-// 1/||key|| per sub-key, for the tensor-core select kernel (which contracts with the keys as stored)
-static int key_inv_norms(peer_op* h, const void* keys0, const void* keys1, cudaStream_t s) {
+// Tensor-core selection: 1/||key|| per sub-key for the kernel itself (it contracts with the keys as stored), the
+// normalised keys for the exact kernel behind it, and the first pass's error bounds, in one launch
+static int key_prep(peer_op* h, const void* keys0, const void* keys1, cudaStream_t s) {
     const peer_config_t& c = h->cfg;
-    const int hw = c.query_dim / 2;
-    CU_TRY(h, launch_key_inv_norms(keys0, c.n_keys0, hw, c.norm_keys, h->invn0, s, h->sel_eps));
-    CU_TRY(h, launch_key_inv_norms(keys1, c.n_keys1, hw, c.norm_keys, h->invn1, s, h->sel_eps ? h->sel_eps + 1 : nullptr));
-    h->launches += 2;
+    CU_TRY(h, launch_key_prep(keys0, keys1, c.n_keys0, c.n_keys1, c.query_dim / 2, c.norm_keys, h->khat0, h->khat1,
+                              h->invn0, h->invn1, h->sel_eps, s));
+    h->launches += 1;
     return PEER_OK;
 }
 
@@ -514,8 +514,7 @@ extern "C" int peer_forward(peer_handle_t h, const peer_tensors_t* t, int64_t n_
     if (rc) return rc;
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, s);
-    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
+    rc = h->general_select ? PEER_OK : (h->use_tc_select ? key_prep(h, t->keys0, t->keys1, s) : normalise_keys(h, t->keys0, t->keys1, s));
     if (rc) return rc;
     const int ab = act_bytes(c.act_dtype);
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
@@ -581,8 +580,7 @@ extern "C" int peer_block_forward(peer_handle_t h, const peer_tensors_t* t, cons
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const size_t ab = static_cast<size_t>(act_bytes(c.act_dtype));
     if (!h->x_ln) CU_TRY(h, cudaMalloc(&h->x_ln, ab * c.max_tokens * c.input_dim));
-    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, s);
-    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
+    rc = h->general_select ? PEER_OK : (h->use_tc_select ? key_prep(h, t->keys0, t->keys1, s) : normalise_keys(h, t->keys0, t->keys1, s));
     if (rc) return rc;
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
     for (int64_t t0 = 0; t0 < n_tokens; t0 += c.max_tokens) {
@@ -610,8 +608,7 @@ static int host_submit(peer_op* h, const peer_tensors_t* t, int64_t n_tokens, in
     dt.x = h->d_x[0]; dt.out = h->d_out[0];
     rc = check_tensors(h, &dt, true);
     if (rc) return rc;
-    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, h->st_run);
-    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, h->st_run);
+    rc = h->general_select ? PEER_OK : (h->use_tc_select ? key_prep(h, t->keys0, t->keys1, h->st_run) : normalise_keys(h, t->keys0, t->keys1, h->st_run));
     if (rc) return rc;
 
     const int ab = act_bytes(c.act_dtype);
@@ -703,8 +700,7 @@ extern "C" int peer_select(peer_handle_t h, const float* queries, const void* ke
         return fail(h, PEER_ERR_UNSUPPORTED, "peer_select takes two sub-key tables; this layer has %d key dimensions: use peer_select_nd", h->nd);
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    int rc = normalise_keys(h, keys0, keys1, s);
-    if (!rc && h->use_tc_select) rc = key_inv_norms(h, keys0, keys1, s);
+    int rc = h->use_tc_select ? key_prep(h, keys0, keys1, s) : normalise_keys(h, keys0, keys1, s);
     if (rc) return rc;
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;
     const int64_t HQ = static_cast<int64_t>(c.num_heads) * c.query_dim;
@@ -741,8 +737,7 @@ extern "C" int peer_select_tokens(peer_handle_t h, const peer_tensors_t* t, int6
     if (rc) return rc;
     const peer_config_t& c = h->cfg;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    rc = h->general_select ? PEER_OK : normalise_keys(h, t->keys0, t->keys1, s);
-    if (!rc && h->use_tc_select) rc = key_inv_norms(h, t->keys0, t->keys1, s);
+    rc = h->general_select ? PEER_OK : (h->use_tc_select ? key_prep(h, t->keys0, t->keys1, s) : normalise_keys(h, t->keys0, t->keys1, s));
     if (rc) return rc;
     const int ab = act_bytes(c.act_dtype);
     const int64_t HK = static_cast<int64_t>(c.num_heads) * c.top_k;

@@ -25,7 +25,7 @@
 // so with normalised queries it contracts two of the three bf16 terms of the
 // query (hi + mid): two thirds of the MMAs.  Dropping lo changes a score by at
 // most eps = 2^-16 ||k|| / max(||k||, 1e-12) (Cauchy-Schwarz with ||q|| = 1; hi and
-// mid each leave a relative remainder of 2^-8 per element; key_inv_norm_kernel
+// mid each leave a relative remainder of 2^-8 per element; key_prep_kernel
 // takes the maximum over the table), and 16 distinct keys reach the 16th
 // largest group maximum t of those scores, so the exact 16th best score is at
 // least t - eps: that is the bound the exact second pass collects against.
@@ -64,6 +64,10 @@
 // bounds, candidate lists, pool), so they synchronise among themselves only
 // (one named barrier per group) and the four groups drift apart by up to the
 // four accumulators in flight.
+// Few rows (a decode-shaped batch, under a wave of 128-row tiles on a quarter of the SMs): tiles of 32 rows.  Four
+// times as many SMs take part; a CTA then contracts with N = 32 and only the first set of four scan warps works,
+// each lane on the same 32 rows per key as before, so a row's scores, bound and candidates - and with them the
+// result - are what the 128-row tiles give.
 // Ordering among exactly equal scores: smaller sub-key index first (per half),
 // smaller candidate position first (final), as in select_simt.cu.
 #include <float.h>
@@ -129,6 +133,7 @@ struct SelTcParams {
     int32_t* overflow_rows; int* overflow_count;   // rows left to the exact kernel
     unsigned long long* stats;                     // optional [2]: pooled row-halves, rows left to the exact kernel
     int fast0;                                     // pass 0 contracts two query terms instead of three
+    int bm;                                        // rows per tile: 128, or 32 for small batches (more CTAs, a quarter of the scan warps each)
     int vec_out;                                   // k == 16 and every output array 16-byte aligned: vector stores
     const float* eps0; const float* eps1;          // fast0: largest error of such a score, per table (device scalars)
 };
@@ -254,11 +259,12 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     auto k_empty = [&](int s) { return bar0 + 8u * (2 + K_STAGES + s); };
     auto acc_full = [&](int a) { return bar0 + 8u * (2 + 2 * K_STAGES + a); };
     auto acc_empty = [&](int a) { return bar0 + 8u * (2 + 2 * K_STAGES + N_ACC + a); };
+    const uint32_t q_box = static_cast<uint32_t>(p.bm) * 128u;          // bytes of one query box: bm rows x 64 bf16
 
     if (tid == 0) {
         mbar_init(q_full, 1); mbar_init(q_empty, 1);
         for (int s = 0; s < K_STAGES; ++s) { mbar_init(k_full(s), 1); mbar_init(k_empty(s), 1); }
-        for (int a = 0; a < N_ACC; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), SCAN_WARPS * 32); }
+        for (int a = 0; a < N_ACC; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), p.bm * 4); }   // the scan threads of the tile's rows
         mbar_fence_init();
         tc::tma_prefetch_desc(&map_q); tc::tma_prefetch_desc(&map_k0); tc::tma_prefetch_desc(&map_k1);
     }
@@ -274,11 +280,12 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     const int hw = p.Q / 2;
     const int KA = hw / 64;                                   // 64-column boxes per half
     const int nch0 = (p.n0 + NC - 1) / NC, nch1 = (p.n1 + NC - 1) / NC;
-    const int64_t n_tiles = (p.rows + BM - 1) / BM;
-    const uint32_t q_bytes = 3u * KA * BOX_BYTES, k_bytes = static_cast<uint32_t>(KA) * BOX_BYTES;
+    const int64_t n_tiles = (p.rows + p.bm - 1) / p.bm;
+    const uint32_t q_bytes = 3u * KA * q_box, k_bytes = static_cast<uint32_t>(KA) * BOX_BYTES;
 
     // The control warps need few registers; the rest of the launch allocation goes to the scan warps.
     if (warp < 4) {
+      // (one value for the four control warps: the warps of a warpgroup must execute the same setmaxnreg)
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(CTRL_REGS));
       if (warp == 0) {
         // ---------------- TMA producer ----------------
@@ -291,8 +298,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     mbar_expect_tx(q_full, q_bytes);
                     for (int t = 0; t < 3; ++t)
                         for (int ka = 0; ka < KA; ++ka)
-                            tc::tma_load_2d(sQ + (t * KA + ka) * BOX_BYTES, &map_q, hf * hw + ka * 64,
-                                            static_cast<int>(t * p.term_rows + tile * BM), q_full);
+                            tc::tma_load_2d(sQ + (t * KA + ka) * q_box, &map_q, hf * hw + ka * 64,
+                                            static_cast<int>(t * p.term_rows + tile * p.bm), q_full);
                     const int nch = hf ? nch1 : nch0;
                     const CUtensorMap* mk = hf ? &map_k1 : &map_k0;
                     for (int c2 = 0; c2 < 2 * nch; ++c2) {          // two passes over the sub-keys
@@ -309,7 +316,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
       } else if (warp == 1) {
         // ---------------- MMA issuer: D[key, row] = sum over the three query terms of K . q^T ----------------
         if (lane == 0) {
-            const uint32_t idesc = tc::idesc_bf16_f32(NC, BM);
+            const uint32_t idesc = tc::idesc_bf16_f32(NC, p.bm);        // a narrow tile contracts its 32 rows only
             uint32_t q_phase = 0; int stage = 0; uint32_t k_phase = 0; uint32_t g = 0; bool ok = true;
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (int hf = 0; hf < 2 && ok; ++hf) {
@@ -327,7 +334,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         for (int t = 0; t < terms; ++t)
                             for (int ka = 0; ka < KA; ++ka) {
                                 const uint64_t kd = tc::smem_desc_sw128(sK + stage * K_STAGE_BYTES + ka * BOX_BYTES);
-                                const uint64_t qd = tc::smem_desc_sw128(sQ + (t * KA + ka) * BOX_BYTES);
+                                const uint64_t qd = tc::smem_desc_sw128(sQ + (t * KA + ka) * q_box);
 #pragma unroll
                                 for (int k = 0; k < 4; ++k) {
                                     tc::umma_bf16(d_tmem, kd + 2 * k, qd + 2 * k, idesc, first);
@@ -352,7 +359,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
         const int half16 = lane & 16;                  // rows 4..7 of a warp keep their lists in lanes 16..31
         uint32_t g = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        for (int64_t tile = blockIdx.x; tile < n_tiles && cg * 32 < p.bm; tile += gridDim.x) {
             // sorted lists of my 8 rows, per half: rows 0-3 in lanes 0-15, rows 4-7 in lanes 16-31
             float hv[2][4]; int hc[2][4];
             unsigned overflow = 0;                     // bit rr: row 8s+rr overflowed its candidate list
@@ -511,7 +518,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                         if (cnt >= LOST) overflow |= 1u << (rb + q);
                         else if (cnt > CAP) {
                             pooled |= 1u << q;
-                            if (p.stats && lane == 0 && tile * BM + row < p.rows) atomicAdd(p.stats, 1ULL);
+                            if (p.stats && lane == 0 && tile * p.bm + row < p.rows) atomicAdd(p.stats, 1ULL);
                         }
                         v[q] = -INFINITY; c[q] = INT_MAX;
                         if (lane < min(cnt, CAP)) { const int2 e = s_cand[row * CAND_PITCH + lane]; v[q] = __int_as_float(e.x); c[q] = e.y; }
@@ -576,7 +583,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                 __syncwarp();
                 const int rr = lane >> 2, sub = lane & 3;
                 const int2* rowm = s_cand + (s * 8 + rr) * CAND_PITCH;
-                const int64_t grow = tile * BM + s * 8 + rr;
+                const int64_t grow = tile * p.bm + s * 8 + rr;
                 const bool lost_row = (overflow >> rr) & 1u;
                 if (grow < p.rows && lost_row && sub == 0) {   // left to the exact kernel
                     p.overflow_rows[atomicAdd(p.overflow_count, 1)] = static_cast<int32_t>(grow);
@@ -669,27 +676,41 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
     if (warp == 0) tc::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// Per sub-key: out[r] = 1 / max(||key||, 1e-12) (or 1).  Optionally also, as a running maximum over the table,
-// eps = 2^-16 * ||key|| * out[r] * (1 + 2^-10) + 1e-6: how much a score can lose when the query's lo term is left
-// out of the contraction (|lo . key| <= ||lo|| ||key||, ||lo|| <= 2^-16 for a unit query half; the last terms
-// cover ||q|| = 1 up to rounding and the fp32 accumulation).
-__global__ void key_inv_norm_kernel(const __nv_bfloat16* __restrict__ keys, int n, int width, int do_norm,
-                                    float* __restrict__ out, float* __restrict__ eps) {
+// What the selection needs of the two sub-key tables, in one launch (one warp per sub-key).  Per sub-key:
+// invn[r] = 1 / max(||key||, 1e-12) (or 1), for the tensor-core kernel, which contracts with the keys as stored;
+// khat[c][r] = key[c] / max(||key||, 1e-12) in fp32, transposed, for the exact kernel that redoes handed-over rows.
+// Optionally also, as a running maximum per table, eps = 2^-16 * ||key|| * invn[r] * (1 + 2^-10) + 1e-6: how much a
+// score can lose when the query's lo term is left out of the contraction (|lo . key| <= ||lo|| ||key||, ||lo|| <=
+// 2^-16 for a unit query half; the last terms cover ||q|| = 1 up to rounding and the fp32 accumulation).
+__global__ void key_prep_kernel(const __nv_bfloat16* __restrict__ keys0, const __nv_bfloat16* __restrict__ keys1,
+                                int n0, int n1, int width, int do_norm, float* __restrict__ khat0,
+                                float* __restrict__ khat1, float* __restrict__ invn0, float* __restrict__ invn1,
+                                float* __restrict__ eps) {
     const int lane = threadIdx.x & 31;
-    const int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (r >= n) return;
+    int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (r >= n0 + n1) return;
+    const int table = r >= n0;
+    if (table) r -= n0;
+    const int n = table ? n1 : n0;
+    const __nv_bfloat16* __restrict__ row = (table ? keys1 : keys0) + static_cast<int64_t>(r) * width;
+    float* __restrict__ khat = table ? khat1 : khat0;
     float ss = 0.f;
     for (int c = lane; c < width; c += 32) {
-        const float v = __bfloat162float(keys[static_cast<int64_t>(r) * width + c]);
+        const float v = __bfloat162float(row[c]);
         ss = fmaf(v, v, ss);
     }
     ss = warp_sum(ss);
-    const float inv = do_norm ? 1.0f / fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
+    const float nrm = do_norm ? fmaxf(sqrtf(ss), 1e-12f) : 1.0f;
+    for (int c = lane; c < width; c += 32) {
+        const float v = __bfloat162float(row[c]);
+        khat[static_cast<int64_t>(c) * n + r] = do_norm ? v / nrm : v;
+    }
+    const float inv = do_norm ? 1.0f / nrm : 1.0f;
     if (lane == 0) {
-        out[r] = inv;
+        (table ? invn1 : invn0)[r] = inv;
         if (eps) {
             const float e = 1.52587890625e-5f * sqrtf(ss) * inv * 1.0009765625f + 1e-6f;
-            atomicMax(reinterpret_cast<int*>(eps), __float_as_int(e));  // positive floats order like their bit patterns
+            atomicMax(reinterpret_cast<int*>(eps + table), __float_as_int(e));  // positive floats order like their bit patterns
         }
     }
 }
@@ -707,14 +728,15 @@ cudaError_t select_tc_setup() {
                                 static_cast<int>(Smem::total));
 }
 
-cudaError_t launch_key_inv_norms(const void* keys, int n, int width, int do_norm, float* out, cudaStream_t s,
-                                 float* eps) {
+cudaError_t launch_key_prep(const void* keys0, const void* keys1, int n0, int n1, int width, int do_norm, float* khat0,
+                            float* khat1, float* invn0, float* invn1, float* eps, cudaStream_t s) {
     if (eps) {
-        const cudaError_t e = cudaMemsetAsync(eps, 0, sizeof(float), s);
+        const cudaError_t e = cudaMemsetAsync(eps, 0, 2 * sizeof(float), s);
         if (e != cudaSuccess) return e;
     }
-    const unsigned blocks = static_cast<unsigned>((static_cast<int64_t>(n) * 32 + 255) / 256);
-    key_inv_norm_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(keys), n, width, do_norm, out, eps);
+    const unsigned blocks = static_cast<unsigned>((static_cast<int64_t>(n0 + n1) * 32 + 255) / 256);
+    key_prep_kernel<<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(keys0), static_cast<const __nv_bfloat16*>(keys1),
+                                           n0, n1, width, do_norm, khat0, khat1, invn0, invn1, eps);
     return cudaGetLastError();
 }
 
@@ -723,8 +745,12 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
     const int hw = a.Q / 2;
     CUtensorMap mq, mk0, mk1;
     const int fast0 = a.eps0 && a.eps1;
+    // Few rows (a decode-shaped batch): tiles of 32 rows, so that four times as many SMs take part and a tile's
+    // chain of chunk steps is shorter (one set of four scan warps, MMAs of N = 32, a deeper key ring).  Same
+    // results: a row's scores, bound and candidates do not depend on which rows share its tile.
+    const int bm = ((a.rows + BM - 1) / BM) * 4 <= a.sm_count ? 32 : BM;
     if (!make_tensor_map_bf16(&mq, a.q_split, static_cast<uint64_t>(3 * a.term_rows), static_cast<uint64_t>(a.Q),
-                              static_cast<uint64_t>(a.Q), BM) ||
+                              static_cast<uint64_t>(a.Q), bm) ||
         !make_tensor_map_bf16(&mk0, a.keys0, static_cast<uint64_t>(a.n0), static_cast<uint64_t>(hw),
                               static_cast<uint64_t>(hw), NC) ||
         !make_tensor_map_bf16(&mk1, a.keys1, static_cast<uint64_t>(a.n1), static_cast<uint64_t>(hw),
@@ -740,7 +766,8 @@ cudaError_t launch_select_tc(const SelectTcArgs& a, cudaStream_t s) {
                                reinterpret_cast<uintptr_t>(a.ids64) | reinterpret_cast<uintptr_t>(a.raw_scores) |
                                reinterpret_cast<uintptr_t>(a.prod_ids);
     p.vec_out = a.k == LK && (out_bits & 15u) == 0;
-    const int64_t n_tiles = (a.rows + BM - 1) / BM;
+    p.bm = bm;
+    const int64_t n_tiles = (a.rows + p.bm - 1) / p.bm;
     const unsigned grid = static_cast<unsigned>(n_tiles < a.sm_count ? n_tiles : a.sm_count);
     select_tc_kernel<<<grid, THREADS, Smem::total, s>>>(mq, mk0, mk1, p);
     return cudaGetLastError();

@@ -26,16 +26,30 @@ from _util import make_op
 pytestmark = pytest.mark.gpu
 
 
-def _run(dev, q, keys, k, mode="product", norm_keys=True, norm_query=True):
-    """q fp32 [T, H, Q], keys two bf16 tables -> (ids, scores, (pooled lists, refined rows), oracle ids, oracle scores)."""
+WIDE_ROWS = 148 * 32 + 64      # batches of more (token, head) rows than this take tiles of 128 rows, smaller ones of 32
+
+
+@pytest.fixture(params=["tiles_of_32_rows", "tiles_of_128_rows"])
+def wide(request):
+    return request.param == "tiles_of_128_rows"
+
+
+def _run(dev, q, keys, k, mode="product", norm_keys=True, norm_query=True, wide=False):
+    """q fp32 [T, H, Q], keys two bf16 tables -> (ids, scores, (pooled lists, refined rows), oracle ids, oracle scores).
+    ``wide``: random filler tokens follow q, enough for the kernel to choose its 128-row tiles; only q's rows are
+    returned and checked."""
     T, H, Q = q.shape
     n = (keys[0].shape[0], keys[1].shape[0])
-    cfg = syn.PeerConfig("seltc", 64, 64, H, Q, n, k, torch.bfloat16, torch.bfloat16, 1, T)
+    q_run = q
+    if wide and T * H <= WIDE_ROWS:
+        q_run = torch.cat([q, _queries((WIDE_ROWS + H) // H - T + 1, H, Q, 999)])
+    cfg = syn.PeerConfig("seltc", 64, 64, H, Q, n, k, torch.bfloat16, torch.bfloat16, 1, q_run.shape[0])
     op = make_op(cfg, dev, mode, norm_keys=norm_keys, norm_query=norm_query)
     op.select_stats()
-    ids, sc = op.select(q.to(dev).contiguous(), keys[0].to(dev), keys[1].to(dev))
+    ids, sc = op.select(q_run.to(dev).contiguous(), keys[0].to(dev), keys[1].to(dev))
     op.query_status()
     stats = op.select_stats()
+    ids, sc = ids[:T], sc[:T]
     kf = [kt.float() for kt in keys]
     with torch.no_grad():
         o_ids, o_sc = orc.select(q.unsqueeze(0), kf, k, n, norm_keys, norm_query, mode)
@@ -71,25 +85,25 @@ def _queries(T, H, Q, seed):
                                              ((129, 1024), 8, 2, 128, 67), ((128, 128), 1, 1, 128, 5),
                                              ((256, 384), 4, 5, 128, 33), ((640, 512), 8, 4, 256, 129)])
 @pytest.mark.parametrize("mode", ["reference", "product"])
-def test_ragged_grids_small_k_and_partial_tiles(cuda_device, n_keys, k, H, Q, T, mode):
+def test_ragged_grids_small_k_and_partial_tiles(cuda_device, n_keys, k, H, Q, T, mode, wide):
     keys = [_keys(n_keys[0], Q // 2, 1), _keys(n_keys[1], Q // 2, 2)]
     q = _queries(T, H, Q, 3 + k)
-    _, _, stats, exact, rows = _run(cuda_device, q, keys, k, mode)
+    _, _, stats, exact, rows = _run(cuda_device, q, keys, k, mode, wide=wide)
     assert exact >= 0.99 * rows
 
 
 @pytest.mark.parametrize("norm_keys,norm_query", [(True, False), (False, True), (False, False)])
-def test_normalisation_switches_on_the_tensor_core_path(cuda_device, norm_keys, norm_query):
+def test_normalisation_switches_on_the_tensor_core_path(cuda_device, norm_keys, norm_query, wide):
     """norm_keys / norm_query off (experts.py:153-163): without unit queries the first pass has no error bound for
     a dropped term and contracts all three; without key normalisation the scale factors are 1."""
     n_keys, k, H, Q, T = (1024, 640), 16, 4, 256, 70
     keys = [_keys(n_keys[0], Q // 2, 5), _keys(n_keys[1], Q // 2, 6)]
     q = _queries(T, H, Q, 7)
-    _, _, _, exact, rows = _run(cuda_device, q, keys, k, "product", norm_keys, norm_query)
+    _, _, _, exact, rows = _run(cuda_device, q, keys, k, "product", norm_keys, norm_query, wide=wide)
     assert exact >= 0.99 * rows
 
 
-def test_identical_keys_overflow_the_list_into_the_pool(cuda_device):
+def test_identical_keys_overflow_the_list_into_the_pool(cuda_device, wide):
     """40 copies of one sub-key, spread over the table: in the rows whose query points at that key all 40
     tie for first place, so the row's candidate list (32 slots) spills into the pool."""
     T, H, Q, n, k = 96, 2, 256, 1024, 16
@@ -99,38 +113,38 @@ def test_identical_keys_overflow_the_list_into_the_pool(cuda_device):
     q = _queries(T, H, Q, 13)
     hot = torch.arange(0, T, 9)                                   # a few rows per tile: the pool (64 entries) suffices
     q[hot, :, :Q // 2] = q[hot, :, :Q // 2] * 0.3 + 4.0 * keys[0][3].float()
-    ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k)
+    ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k, wide=wide)
     assert pooled > 0, "the pool path did not fire"
     # the hot rows' best 16 all carry a copy of the duplicated key in dimension 0
     i0 = ids[hot] // n
     assert bool(torch.isin(i0, dup).all())
 
 
-def test_hundreds_of_identical_keys_fill_the_pool_and_rows_are_redone_exactly(cuda_device):
+def test_hundreds_of_identical_keys_fill_the_pool_and_rows_are_redone_exactly(cuda_device, wide):
     T, H, Q, n, k = 40, 4, 256, 1024, 16
     keys = [_keys(n, Q // 2, 21), _keys(n, Q // 2, 22)]
     dup = torch.arange(300) * 3 + 1
     keys[1][dup] = keys[1][1].clone()
     q = _queries(T, H, Q, 23)
     q[:, :, Q // 2:] = q[:, :, Q // 2:] * 0.3 + 4.0 * keys[1][1].float()      # every row ties 300 ways
-    ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k)
+    ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k, wide=wide)
     assert refined > 0, "no row went to the exact kernel"
     assert bool(torch.isin(ids % n, dup).all())
 
 
-def test_a_popular_key_exceeds_one_lanes_staging_slots(cuda_device):
+def test_a_popular_key_exceeds_one_lanes_staging_slots(cuda_device, wide):
     """One key that scores in the top 16 of every row: the scan lane that owns it has a hit in all 32 of
     its rows in one chunk, more than its 8 staging slots, so those rows go to the exact kernel."""
     T, H, Q, n, k = 64, 2, 128, 512, 8
     keys = [_keys(n, Q // 2, 31), _keys(n, Q // 2, 32)]
     q = _queries(T, H, Q, 33)
     q[:, :, :Q // 2] += 6.0 * keys[0][77].float()            # cosine with key 77 around 0.6 in every row
-    ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k)
+    ids, sc, (pooled, refined), _, _ = _run(cuda_device, q, keys, k, wide=wide)
     assert refined > 0, "the staging-slot overflow did not fire"
     assert float(((ids // n) == 77).any(-1).float().mean()) > 0.9
 
 
-def test_clustered_scores_without_exact_ties(cuda_device):
+def test_clustered_scores_without_exact_ties(cuda_device, wide):
     """Keys drawn around a few centres (what trained sub-keys look like, unlike N(0, 1/d) noise): many
     scores sit just under each row's bound."""
     T, H, Q, n, k = 130, 4, 256, 1024, 16
@@ -141,8 +155,21 @@ def test_clustered_scores_without_exact_ties(cuda_device):
         which = torch.randint(0, 8, (n,), generator=g)
         keys.append((centres[which] + 0.05 * torch.randn(n, Q // 2, generator=g)).bfloat16())
     q = _queries(T, H, Q, 43)
-    _, _, (pooled, refined), exact, rows = _run(cuda_device, q, keys, k)
+    _, _, (pooled, refined), exact, rows = _run(cuda_device, q, keys, k, wide=wide)
     assert pooled + refined > 0
+
+
+def test_both_tile_shapes_give_the_same_lists(cuda_device):
+    """A row's result does not depend on the rows it shares a tile with: the same queries alone (tiles of 32
+    rows) and followed by filler tokens (tiles of 128 rows), bit for bit, tied rows included."""
+    T, H, Q, n, k = 90, 4, 256, (1024, 640), 16
+    keys = [_keys(n[0], Q // 2, 61), _keys(n[1], Q // 2, 62)]
+    keys[0][torch.arange(20) * 40 + 7] = keys[0][7].clone()       # some exact ties
+    q = _queries(T, H, Q, 63)
+    q[::5, :, :Q // 2] = q[::5, :, :Q // 2] * 0.3 + 4.0 * keys[0][7].float()
+    ids_a, sc_a, _, _, _ = _run(cuda_device, q, keys, k, wide=False)
+    ids_b, sc_b, _, _, _ = _run(cuda_device, q, keys, k, wide=True)
+    assert torch.equal(ids_a, ids_b) and torch.equal(sc_a, sc_b)
 
 
 def test_stage_entry_equals_whole_layer_selection(cuda_device):
