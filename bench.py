@@ -587,6 +587,26 @@ def run_c4(env, steps):
         "bandwidth_floor_us": gathered / world / (peak * 1e9) * 1e6,
         "collectives": "all_gather(x), all_to_all(tuple buckets), reduce_scatter(fp32 partial sums); NCCL, NVLS off",
     })
+    # ---- the same step with the library's direct exchange (stores into the peers' memory, no collective)
+    try:
+        direct = ShardedPEER(layer.layer, None, exchange="direct")
+        yd = direct(xl)
+        direct.check_exchange()
+        close = float((yd.float() - y.float()).abs().max())
+        for _ in range(5):
+            direct(xl)
+        med_d, all_d = time_steps(env, lambda: direct(xl), steps)
+        direct.check_exchange()
+        worst = env.max_over_ranks([close])
+        out["direct_exchange"] = {"ms_per_step": med_d / steps, "tokens_per_s": cfg.tokens / (med_d / steps / 1e3),
+                                  "repeats_ms": all_d, "max_abs_diff_to_collective_form": worst[0],
+                                  "agrees": bool(worst[0] <= 2e-3),
+                                  "what": "x, tuple blocks and fp32 partial sums written into the peers' memory over NVLink "
+                                          "(CUDA IPC mappings, plain stores, step numbers as flags, bounded waits); "
+                                          "partial sums added in rank order"}
+        direct.close()
+    except RuntimeError as e:                     # raised on every rank or on none (the set-up agrees on it)
+        out["direct_exchange"] = {"unavailable": str(e)[:200]}
     del layer, down, up
     torch.cuda.empty_cache()
     return out

@@ -234,6 +234,46 @@ int peer_gather_eval_routed(peer_handle_t h, const void* x, const int32_t* recv,
                             const float* down_scale, const float* up_scale, int64_t n_local_rows,
                             float* out_f32, void* stream);
 
+/* Direct exchange for the expert-parallel layer on the GPUs of one node: what the all-gather, the all-to-all
+ * and the reduce-scatter around peer_select_tokens / peer_gather_eval_routed move, written by plain stores
+ * into the peers' memory (NVLink) with step numbers as completion flags.  No counterpart in the reference
+ * (it has no sharded PEER: docs/paper/paper.tex:446, docs/CUTLASS_KERNEL.md:181).
+ *
+ * peer_xchg_create allocates this rank's region on the current device (activations of all world*T tokens,
+ * `world` tuple blocks in the format of peer_route_tuples, `world` slots of fp32 partial sums for this rank's
+ * T tokens, each twice, and the flags); peer_xchg_export gives its 64-byte CUDA IPC handle; after the ranks
+ * have exchanged the handles by any host-side means, peer_xchg_attach(handles of all ranks, 64 bytes each,
+ * in rank order; the own entry is ignored) maps the peers' regions.  One step, all calls on one stream:
+ *   peer_xchg_push_x(x of my T tokens)           -> starts the step; x goes to every rank
+ *   peer_xchg_route(ids, weights [T, E])         -> tuples go to the owners of the rows (after peer_select_tokens)
+ *   peer_xchg_wait_inputs(&x_all, &recv)         -> waits for all ranks' x and tuples; the pointers are what
+ *                                                   peer_gather_eval_routed takes
+ *   peer_xchg_combine(partial [world*T, D_out] fp32, out [T, D_out] act dtype)
+ *                                                -> partial sums go to the tokens' ranks; out = their sum in
+ *                                                   rank order (deterministic), cast to the activation dtype
+ * peer_xchg_forward is that whole step in one call (t->x = my T tokens, t->expert_down / expert_up = my rows; the
+ * scratch buffers are the caller's: ids and weights [T, E], partial sums fp32 [world*T, D_out]).
+ * peer_xchg_counts (after peer_xchg_wait_inputs) copies out how many tuples each of the world*T tokens brought
+ * to this rank.  Every rank must run the same steps in the same order.  Waits are bounded (two seconds): when a rank's data
+ * does not arrive, the step's result is undefined and peer_xchg_status (synchronises the stream) returns
+ * PEER_ERR_DEVICE_TIMEOUT; nothing hangs.  peer_xchg_destroy must be called by all ranks only after all of
+ * them have finished their last step (a host barrier), since peers write into the region.  Errors: return
+ * code + peer_last_error(NULL). */
+typedef struct peer_xchg* peer_xchg_t;
+int peer_xchg_create(int32_t world, int32_t rank, int64_t tokens_per_rank, int32_t entries_per_token,
+                     int32_t input_dim, int32_t output_dim, int32_t act_dtype, peer_xchg_t* out);
+int peer_xchg_export(peer_xchg_t h, unsigned char* handle64);
+int peer_xchg_attach(peer_xchg_t h, const unsigned char* handles);
+int peer_xchg_push_x(peer_xchg_t h, const void* x_local, void* stream);
+int peer_xchg_route(peer_xchg_t h, const int32_t* ids, const float* weights, int64_t rows_per_rank, void* stream);
+int peer_xchg_wait_inputs(peer_xchg_t h, const void** x_all, const int32_t** recv, void* stream);
+int peer_xchg_combine(peer_xchg_t h, const float* partial, void* out, void* stream);
+int peer_xchg_forward(peer_xchg_t x, peer_handle_t h, const peer_tensors_t* t, int32_t* ids_scratch,
+                      float* weights_scratch, int64_t rows_per_rank, float* partial_scratch, void* out, void* stream);
+int peer_xchg_counts(peer_xchg_t h, int32_t* counts_out, void* stream);
+int peer_xchg_status(peer_xchg_t h, void* stream);
+int peer_xchg_destroy(peer_xchg_t h);
+
 /* Backward of peer_gather_eval: the gradients autograd derives for the expert evaluation of the
  * reference (llm/models/experts.py:332-382; exercised by tests/test_peer_integration.py:181-192 and
  * by the training step, llm/training/train.py:743-768).  Given grad_out = dL/dout [T, output_dim]

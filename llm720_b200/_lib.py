@@ -66,6 +66,19 @@ EXPORTS = {
                                                                                            C.c_int64, C.c_void_p]),
     "peer_gather_eval_backward": (C.c_int, [C.c_void_p] * 11 + [C.c_int32, C.c_int64, C.c_void_p]),
     "peer_gather_eval_backward_rows": (C.c_int, [C.c_void_p] * 11 + [C.c_int32, C.c_int64, C.c_int64, C.c_void_p]),
+    "peer_xchg_create": (C.c_int, [C.c_int32, C.c_int32, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                   C.POINTER(C.c_void_p)]),
+    "peer_xchg_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "peer_xchg_attach": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "peer_xchg_push_x": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "peer_xchg_route": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "peer_xchg_wait_inputs": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_void_p]),
+    "peer_xchg_combine": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "peer_xchg_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(PeerTensors), C.c_void_p, C.c_void_p, C.c_int64,
+                                    C.c_void_p, C.c_void_p, C.c_void_p]),
+    "peer_xchg_counts": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p]),
+    "peer_xchg_status": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "peer_xchg_destroy": (C.c_int, [C.c_void_p]),
     "peer_usage_histogram": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_query_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "peer_launch_count": (C.c_int64, [C.c_void_p]),

@@ -200,9 +200,12 @@ class ShardedPEER:
     (`expert_down.weight` / `expert_up.weight` of shape [num_experts/world, D]);
     `num_experts` and `product_key_dim` describe the FULL table."""
 
-    def __init__(self, layer, group=None):
-        self.layer, self.group = layer, group
+    def __init__(self, layer, group=None, exchange: str = "nccl"):
+        if exchange not in ("nccl", "direct"):
+            raise ValueError("exchange is 'nccl' (three collectives) or 'direct' (stores into the peers' memory)")
+        self.layer, self.group, self.exchange = layer, group, exchange
         self._buf, self._buf_key, self.last_counts = None, None, None
+        self._xchg = None                 # direct exchange: the library's handle of this rank's region
         self.world = dist.get_world_size(group)
         self.rows = rows_per_rank(layer.num_experts, self.world)
         if layer.expert_down.weight.shape[0] != self.rows:
@@ -210,7 +213,7 @@ class ShardedPEER:
 
     @classmethod
     def build(cls, module_kwargs: dict, small_weights: dict, down_local: torch.Tensor, up_local: torch.Tensor,
-              group=None, index_mode: str = "product", down_scale=None, up_scale=None):
+              group=None, index_mode: str = "product", down_scale=None, up_scale=None, exchange: str = "nccl"):
         """Assemble the layer from replicated small weights (state-dict names of the module) and this
         rank's table rows, without ever materialising the full tables."""
         from .peer import PEER
@@ -223,7 +226,7 @@ class ShardedPEER:
         layer.expert_down_scale, layer.expert_up_scale = down_scale, up_scale
         layer.eval().requires_grad_(False)
         layer.index_mode = index_mode
-        return cls(layer, group)
+        return cls(layer, group, exchange)
 
     @torch.no_grad()
     def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
@@ -245,8 +248,10 @@ class ShardedPEER:
             self._buf_key = key
         b = self._buf
         stream = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
-        dist.all_gather_into_tensor(b["x_all"], x, group=self.group)
         lib, h = op.lib, op.handle
+        if self.exchange == "direct":
+            return self._forward_direct(x, b, lib, h, stream, T, HK).view(B, S, -1)
+        dist.all_gather_into_tensor(b["x_all"], x, group=self.group)
         # this rank's rows of x_all are x: the selection reads them there, so every pointer below is fixed
         _lib.check(lib.peer_select_tokens(h, b["tensors_ref"], T, b["ids_p"], b["wts_p"], stream), h)
         _lib.check(lib.peer_route_tuples(b["ids_p"], b["wts_p"], T, HK, self.rows, world, b["send_p"], stream), None)
@@ -256,6 +261,81 @@ class ShardedPEER:
         self.last_counts = b["counts_view"]          # tuples this rank evaluated, per token (device tensor)
         out = reduce_scatter_rows(b["partial"], self.group)
         return out.to(hidden_states.dtype).view(B, S, -1)
+
+    def _forward_direct(self, x, b, lib, h, stream, T, HK):
+        """One step with the library's direct exchange (`peer_xchg_*`): x, the tuples and the partial sums go
+        to the peers by stores into their memory; no collective is called.  Waits on a peer are bounded on
+        the device; `check_exchange()` reports one that ran out."""
+        b["tensors"].x = x.data_ptr()                 # the selection reads the caller's tensor
+        out = torch.empty(T, self.layer.output_dim, dtype=x.dtype, device=x.device)
+        _lib.check(lib.peer_xchg_forward(self._xchg, h, b["tensors_ref"], b["ids_p"], b["wts_p"], self.rows,
+                                         b["partial_p"], C.c_void_p(out.data_ptr()), stream), None)
+        self.last_counts = None                       # read on demand: received_counts()
+        return out
+
+    def received_counts(self) -> torch.Tensor:
+        """int32 [world, T]: how many tuples each token brought to this rank in the last step."""
+        if self._xchg is None:
+            return self.last_counts
+        b = self._buf
+        dev = b["counts"].device
+        stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().peer_xchg_counts(self._xchg, C.c_void_p(b["counts"].data_ptr()), stream), None)
+        return b["counts"]
+
+    def check_exchange(self) -> None:
+        """Direct exchange only: synchronises the stream and raises if a wait for a peer's data ran out."""
+        if self._xchg is not None:
+            dev = self.layer.expert_down.weight.device
+            stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+            with torch.cuda.device(dev):
+                _lib.check(_lib.load().peer_xchg_status(self._xchg, stream), None)
+
+    def close(self) -> None:
+        """Releases the direct exchange's region.  Collective: every rank calls it, after its last step."""
+        if self._xchg is not None:
+            torch.cuda.synchronize()
+            dist.barrier(self.group)              # no peer still writes into the region
+            _lib.load().peer_xchg_destroy(self._xchg)
+            self._xchg = None
+            self._buf_key = None
+
+    def _plan_direct(self, T, D, dtype, dev):
+        """The rank's exchange region for this step shape: created, its IPC handle exchanged over the process
+        group (host side), the peers' regions mapped.  Collective; if any rank fails, every rank raises."""
+        from .peer import _DT
+        lib = _lib.load()
+        if self._xchg is not None:
+            self.close()
+        L, world, rank = self.layer, self.world, dist.get_rank(self.group)
+        xh, err, mine = C.c_void_p(), None, b""
+        with torch.cuda.device(dev):
+            try:
+                _lib.check(lib.peer_xchg_create(world, rank, T, L.num_heads * L.num_experts_per_tok, D, L.output_dim,
+                                                _DT[dtype], C.byref(xh)), None)
+                buf = (C.c_ubyte * 64)()
+                _lib.check(lib.peer_xchg_export(xh, buf), None)
+                mine = bytes(buf)
+            except (RuntimeError, ValueError) as e:
+                err = e
+            handles = [None] * world
+            dist.all_gather_object(handles, mine, group=self.group)
+            if err is None:
+                if all(len(hb) == 64 for hb in handles):
+                    try:
+                        _lib.check(lib.peer_xchg_attach(xh, b"".join(handles)), None)
+                    except (RuntimeError, ValueError) as e:
+                        err = e
+                else:
+                    err = RuntimeError("a peer could not create its exchange region")
+            bad = torch.tensor([0 if err is None else 1], device=dev)
+            dist.all_reduce(bad, op=dist.ReduceOp.MAX, group=self.group)   # also: every region is mapped before anyone writes
+            if int(bad):
+                if xh.value:
+                    lib.peer_xchg_destroy(xh)
+                raise RuntimeError(f"direct exchange unavailable: {err if err is not None else 'a peer failed to set it up'}")
+        self._xchg = xh
 
     def _plan(self, op, w, T, D, dtype, dev):
         """Buffers and pre-built C arguments of one step shape: a step is then three collectives and three library
@@ -275,7 +355,10 @@ class ShardedPEER:
         self._buf = dict(x_all=x_all, send=send, recv=recv, partial=partial, ids=ids, wts=wts, tensors=tensors,
                          tensors_ref=C.byref(tensors), ids_p=vp(ids), wts_p=vp(wts), send_p=vp(send), recv_p=vp(recv),
                          x_all_p=vp(x_all), partial_p=vp(partial), down_p=vp(w["expert_down"]), up_p=vp(w["expert_up"]),
-                         ds_p=vp(w["down_scale"]), us_p=vp(w["up_scale"]), counts_view=recv[:, 2 * T * HK:])
+                         ds_p=vp(w["down_scale"]), us_p=vp(w["up_scale"]), counts_view=recv[:, 2 * T * HK:],
+                         counts=torch.zeros(world, T, dtype=torch.int32, device=dev))
+        if self.exchange == "direct":
+            self._plan_direct(T, D, dtype, dev)
 
     def nvlink_bytes_per_step(self, tokens_per_rank: int) -> dict:
         """Bytes each rank SENDS per step, by collective (fixed-shape buckets: the all-to-all carries

@@ -6,6 +6,9 @@
 Every rank holds a row shard of the tables of a decode-shaped layer (d_model 4096, 16 heads,
 query_dim 256, top-k 16, product-key ids); the result must equal the single-device layer that
 rank 0 evaluates on the concatenated batch with the full tables.  Also times the sharded step.
+CHECK_EXCHANGE=direct runs the layer with the library's direct exchange (stores into the peers' memory
+instead of the three collectives) and also compares it with the collective form: same tuples per token,
+outputs equal up to the order in which the ranks' partial sums are added.
 """
 import os
 import sys
@@ -39,10 +42,23 @@ def main():
     else:
         down = syn.make_table_shard(cfg, "expert_down", rank * rows, rows, 4, dev)
         up = syn.make_table_shard(cfg, "expert_up", rank * rows, rows, 4, dev)
-    layer = ShardedPEER.build(cfg.module_kwargs(), sd, down, up)
+    mode = os.environ.get("CHECK_EXCHANGE", "nccl")
+    layer = ShardedPEER.build(cfg.module_kwargs(), sd, down, up, exchange=mode)
     xl = x.view(cfg.tokens, 1, -1)[rank * t_local:(rank + 1) * t_local].contiguous()
     out = layer(xl)
     layer.layer._op.query_status()
+    layer.check_exchange()
+    same = True
+    if mode == "direct":
+        counts = layer.received_counts().clone()
+        other = ShardedPEER.build(cfg.module_kwargs(), sd, down, up, exchange="nccl")
+        out_nccl = other(xl)
+        same = bool(torch.equal(counts.view(-1), other.received_counts().reshape(-1).to(counts.dtype)))
+        same = same and bool(torch.allclose(out.float(), out_nccl.float(), rtol=0, atol=2e-3))
+        for _ in range(3):                       # both parities of the region, and a repeat: same result every step
+            again = layer(xl)
+            same = same and bool(torch.equal(again, out))
+        layer.check_exchange()
 
     err = mag = 0.0
     if compare:
@@ -56,7 +72,7 @@ def main():
         err = float((out.float() - ref.float()).abs().max())
         mag = float(ref.float().abs().max())
     finite = bool(torch.isfinite(out.float()).all()) and float(out.float().abs().max()) > 0
-    ok = torch.tensor([1 if (err <= 2e-2 and finite) else 0], device=dev)
+    ok = torch.tensor([1 if (err <= 2e-2 and finite and same) else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
 
     # timing: per-layer latency of the sharded step (max over ranks, CUDA events)
@@ -72,8 +88,10 @@ def main():
     torch.cuda.synchronize()
     ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    layer.check_exchange()
+    layer.close()
     if rank == 0:
-        print(f"sharded PEER x{world}: experts {cfg.num_experts}, tokens {cfg.tokens}, "
+        print(f"sharded PEER x{world} ({mode} exchange): experts {cfg.num_experts}, tokens {cfg.tokens}, "
               f"{'compared with the single-device layer: ' if compare else 'timing only; '}max-abs err {err:.3g} "
               f"(|ref| max {mag:.3g}), {float(ms):.3f} ms/step, {cfg.tokens / float(ms) * 1e3:.0f} tokens/s, "
               f"{'OK' if int(ok) else 'MISMATCH'}")

@@ -59,3 +59,19 @@ def test_create_rejects_bad_arguments_without_a_device():
     cfg.n_keys1 = 5
     assert lib.peer_create(C.byref(cfg), C.byref(h)) == _lib.ERR_INVALID_ARG
     assert not h.value
+
+
+def test_exchange_create_rejects_bad_arguments_without_a_device():
+    lib = _lib.load()
+    h = C.c_void_p()
+    bf16 = _lib.DTYPE_BF16
+    assert lib.peer_xchg_create(0, 0, 8, 256, 4096, 4096, bf16, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert lib.peer_xchg_create(2, 2, 8, 256, 4096, 4096, bf16, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert lib.peer_xchg_create(17, 0, 8, 256, 4096, 4096, bf16, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert b"world" in lib.peer_last_error(None)
+    assert lib.peer_xchg_create(2, 0, 8, 256, 4097, 4096, bf16, C.byref(h)) == _lib.ERR_UNSUPPORTED
+    assert lib.peer_xchg_create(2, 0, 8, 256, 4096, 4096, 9, C.byref(h)) == _lib.ERR_INVALID_ARG
+    assert h.value is None
+    assert lib.peer_xchg_push_x(None, None, None) == _lib.ERR_INVALID_ARG
+    assert lib.peer_xchg_destroy(None) == _lib.OK
+

@@ -10,12 +10,13 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def test_expert_parallel_layer_on_two_gpus(cuda_device):
+@pytest.mark.parametrize("exchange,port", [("nccl", "29611"), ("direct", "29613")])
+def test_expert_parallel_layer_on_two_gpus(cuda_device, exchange, port):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", CHECK_EXCHANGE=exchange)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                        "--master-addr", "127.0.0.1", "--master-port", "29611",
+                        "--master-addr", "127.0.0.1", "--master-port", port,
                         os.path.join(ROOT, "tests", "multi_gpu_check.py")],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
