@@ -18,6 +18,10 @@ the layer for tables that do not fit, or should not be replicated, on every GPU:
      sums per token);
   5. reduce-scatter of the partial sums gives every rank the outputs of its own tokens.
 
+`ShardedPEER(exchange="direct")` does steps 1, 3 and 5 without collectives: the library's `peer_xchg_*` entries
+store x, the tuple blocks and the partial sums straight into the peers' memory (regions mapped through CUDA
+IPC, step numbers as completion flags, bounded waits) and add the partial sums in rank order.
+
 Result: identical to the single-device layer on the concatenated batch, up to fp32 summation
 order.  The exchange logic exists twice: as plain tensor code (`route_tuples_blocks`,
 `lists_from_blocks`, and the variable-length `route_tuples` / `pack_received`) that runs on any device
