@@ -411,8 +411,8 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                             }
                             const int nh = __popc(myhits);
                             int taken = 0;
-                            while (__any_sync(FULL_MASK, myhits != 0)) {
-                                if (myhits) {
+                            while (myhits) {
+                                {
                                     const int row = cg * 32 + __ffs(myhits) - 1;
                                     myhits &= myhits - 1;
                                     if (taken < STAGE_CAP - 1 || nh <= STAGE_CAP) {
@@ -431,6 +431,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                                     ++taken;
                                 }
                             }
+                            __syncwarp();
                         }
                     }
                     if (pass == 0) {
