@@ -256,7 +256,8 @@ int peer_gather_eval_routed(peer_handle_t h, const void* x, const int32_t* recv,
  * peer_xchg_counts (after peer_xchg_wait_inputs) copies out how many tuples each of the world*T tokens brought
  * to this rank.  Every rank must run the same steps in the same order.  Waits are bounded (two seconds): when a rank's data
  * does not arrive, the step's result is undefined and peer_xchg_status (synchronises the stream) returns
- * PEER_ERR_DEVICE_TIMEOUT; nothing hangs.  peer_xchg_destroy must be called by all ranks only after all of
+ * PEER_ERR_DEVICE_TIMEOUT; nothing hangs.  After such a timeout the ranks' step numbers no longer agree: destroy
+ * the exchange on every rank and create it anew.  peer_xchg_destroy must be called by all ranks only after all of
  * them have finished their last step (a host barrier), since peers write into the region.  Errors: return
  * code + peer_last_error(NULL). */
 typedef struct peer_xchg* peer_xchg_t;

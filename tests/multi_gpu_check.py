@@ -9,6 +9,9 @@ rank 0 evaluates on the concatenated batch with the full tables.  Also times the
 CHECK_EXCHANGE=direct runs the layer with the library's direct exchange (stores into the peers' memory
 instead of the three collectives) and also compares it with the collective form: same tuples per token,
 outputs equal up to the order in which the ranks' partial sums are added.
+CHECK_EXCHANGE=direct_timeout: the last rank sits one step out (it is idle between steps, nothing of its own in
+flight); the others' bounded waits run out after two seconds and show as an error code, nothing hangs; the
+exchange is then closed and built anew, and the next step is right again.
 """
 import os
 import sys
@@ -43,8 +46,10 @@ def main():
         down = syn.make_table_shard(cfg, "expert_down", rank * rows, rows, 4, dev)
         up = syn.make_table_shard(cfg, "expert_up", rank * rows, rows, 4, dev)
     mode = os.environ.get("CHECK_EXCHANGE", "nccl")
-    layer = ShardedPEER.build(cfg.module_kwargs(), sd, down, up, exchange=mode)
     xl = x.view(cfg.tokens, 1, -1)[rank * t_local:(rank + 1) * t_local].contiguous()
+    if mode == "direct_timeout":
+        return missing_rank(cfg, sd, down, up, xl, rank, world, dev)
+    layer = ShardedPEER.build(cfg.module_kwargs(), sd, down, up, exchange=mode)
     out = layer(xl)
     layer.layer._op.query_status()
     layer.check_exchange()
@@ -95,6 +100,34 @@ def main():
               f"{'compared with the single-device layer: ' if compare else 'timing only; '}max-abs err {err:.3g} "
               f"(|ref| max {mag:.3g}), {float(ms):.3f} ms/step, {cfg.tokens / float(ms) * 1e3:.0f} tokens/s, "
               f"{'OK' if int(ok) else 'MISMATCH'}")
+    dist.destroy_process_group()
+    sys.exit(0 if int(ok) else 1)
+
+
+def missing_rank(cfg, sd, down, up, xl, rank, world, dev):
+    layer = ShardedPEER.build(cfg.module_kwargs(), sd, down, up, exchange="direct")
+    good = layer(xl)
+    layer.check_exchange()
+    dist.barrier()
+    noticed = True
+    if rank != world - 1:                      # the last rank does not take part in this step
+        layer(xl)
+        try:
+            layer.check_exchange()
+            noticed = False
+        except RuntimeError as e:
+            noticed = "did not arrive" in str(e)
+    dist.barrier()                             # host side: every rank is between steps
+    layer.close()
+    fresh = ShardedPEER.build(cfg.module_kwargs(), sd, down, up, exchange="direct")
+    again = fresh(xl)
+    fresh.check_exchange()
+    ok = torch.tensor([1 if (noticed and torch.equal(again, good)) else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    fresh.close()
+    if rank == 0:
+        print(f"sharded PEER x{world} (direct exchange, one rank missing a step): the others' waits ran out and were "
+              f"reported, the rebuilt exchange gives the same result: {'OK' if int(ok) else 'MISMATCH'}")
     dist.destroy_process_group()
     sys.exit(0 if int(ok) else 1)
 

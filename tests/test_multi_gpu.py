@@ -10,7 +10,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("exchange,port", [("nccl", "29611"), ("direct", "29613")])
+@pytest.mark.parametrize("exchange,port", [("nccl", "29611"), ("direct", "29613"), ("direct_timeout", "29615")])
 def test_expert_parallel_layer_on_two_gpus(cuda_device, exchange, port):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
