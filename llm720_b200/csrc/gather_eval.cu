@@ -29,20 +29,21 @@ constexpr int MAX_SMEM = 227 * 1024;
 
 // Warps per CTA (one CTA per SM) and ring bytes per warp.  Rows of a 16-bit or 32-bit table keep the memory
 // system busy with 8 warps; FP8 rows carry half the bytes per decoded element, so that instance is bound by
-// instruction issue and runs 14 warps with smaller rings and packed f16 activations (127 registers).
+// the time one warp needs for a row pair's instructions and runs 16 warps (all that 128 registers per thread
+// allow) with smaller rings and packed f16 activations.
 // W10 (bf16 rows of 4 KB only): ten warps on 20 KB rings, for layers whose selected rows stay L2-resident (the
 // reference's id arithmetic addresses at most n0 + n1 - 1 rows): there the stage is bound by instruction issue, not
 // by memory, and more warps help; with rows streaming from HBM eight warps on deeper rings are faster.
-template <typename TT, int CH, bool W10> struct WarpCfg {
-    static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 14 warps
+template <typename TT, int CH, bool W10, bool TIER = false> struct WarpCfg {
+    static constexpr bool MANY = sizeof(TT) == 1 && CH <= 4;      // rows up to 2048 elements: registers allow 16 warps
     static constexpr bool TEN = W10 && sizeof(TT) == 2 && CH == 8;
-    static constexpr int WARPS = MANY ? 14 : (TEN ? 10 : 8);
+    static constexpr int WARPS = MANY ? (TIER ? 14 : 16) : (TEN ? 10 : 8);   // TIER: its slot map needs the shared memory of two warps
     static constexpr int RING_BYTES = MANY ? 12 * 1024 : (TEN ? 20 * 1024 : 24 * 1024);
 };
 
-template <typename TT, int CH, bool W10> struct RingCfg {
+template <typename TT, int CH, bool W10, bool TIER = false> struct RingCfg {
     static constexpr int SLOT = CH * 512;   // bytes: one row of up to CH 16-byte chunks per lane
-    static constexpr int ST0 = WarpCfg<TT, CH, W10>::RING_BYTES / SLOT;
+    static constexpr int ST0 = WarpCfg<TT, CH, W10, TIER>::RING_BYTES / SLOT;
     static constexpr int STAGES = ST0 > MAX_STAGES ? MAX_STAGES : (ST0 < 2 ? 2 : ST0);
 };
 
@@ -174,9 +175,9 @@ struct GatherParams {
 };
 
 template <typename XT, typename TT, int CH, bool W10, bool TIER>
-__global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_eval_kernel(const GatherParams p) {
-    using RC = RingCfg<TT, CH, W10>;
-    constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
+__global__ void __launch_bounds__(WarpCfg<TT, CH, W10, TIER>::WARPS * 32, 1) gather_eval_kernel(const GatherParams p) {
+    using RC = RingCfg<TT, CH, W10, TIER>;
+    constexpr int WARPS = WarpCfg<TT, CH, W10, TIER>::WARPS;
     constexpr int STAGES = RC::STAGES;
     constexpr int SLOT = RC::SLOT;
     constexpr int EPC = Chunk<TT>::N;            // elements per 16-byte chunk
@@ -245,7 +246,7 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
         // bf16 tables with bf16 activations: the activations stay packed and the down-row dot product runs on
         // mixed-precision FMAs (no widening of either operand)
         constexpr bool BFDOT = sizeof(TT) == 2 && sizeof(XT) == 2;
-        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH, W10>::MANY && sizeof(XT) == 2) || BFDOT;
+        constexpr bool PACKX = (CH * EPC > 64) || (WarpCfg<TT, CH, W10, TIER>::MANY && sizeof(XT) == 2) || BFDOT;
         // FP8 rows: the activations are kept as f16 pairs, scaled by a power of two so
         // that the row's largest magnitude lies in [1, 2) (a bf16 value then converts exactly unless it is more
         // than 2^14 times smaller than the largest), and the down-row dot product runs on mixed-precision FMAs.
@@ -449,8 +450,8 @@ __global__ void __launch_bounds__(WarpCfg<TT, CH, W10>::WARPS * 32, 1) gather_ev
 
 template <typename XT, typename TT, int CH, bool W10, bool TIER>
 size_t smem_bytes(int HK) {
-    using RC = RingCfg<TT, CH, W10>;
-    constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
+    using RC = RingCfg<TT, CH, W10, TIER>;
+    constexpr int WARPS = WarpCfg<TT, CH, W10, TIER>::WARPS;
     return static_cast<size_t>(WARPS) * RC::STAGES * RC::SLOT + WARPS * RC::STAGES * 8 +
            static_cast<size_t>(WARPS) * HK * ((sizeof(TT) == 1 ? 16 : 8) + (TIER ? 4 : 0));
 }
@@ -471,7 +472,7 @@ cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
         if (e != cudaSuccess) return e;
         if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
     }
-    constexpr int WARPS = WarpCfg<TT, CH, W10>::WARPS;
+    constexpr int WARPS = WarpCfg<TT, CH, W10, TIER>::WARPS;
     int64_t ctas = (a.T + WARPS - 1) / WARPS;
     if (ctas > a.sm_count) ctas = a.sm_count;
     GatherParams q = p;
@@ -480,7 +481,7 @@ cudaError_t launch_w(const GatherArgs& a, const GatherParams& p, cudaStream_t s)
     // (only for the partial evaluation of a row shard: the ordinary layer keeps one warp per token at every batch
     // size, so that a token's result never depends on how many tokens came with it)
     q.split = a.counts != nullptr && a.T <= a.sm_count &&
-              static_cast<size_t>(WARPS) * a.Dout * sizeof(float) <= static_cast<size_t>(WARPS) * RingCfg<TT, CH, W10>::STAGES * RingCfg<TT, CH, W10>::SLOT;
+              static_cast<size_t>(WARPS) * a.Dout * sizeof(float) <= static_cast<size_t>(WARPS) * RingCfg<TT, CH, W10, TIER>::STAGES * RingCfg<TT, CH, W10, TIER>::SLOT;
     if (q.split) ctas = a.T;
     gather_eval_kernel<XT, TT, CH, W10, TIER><<<static_cast<unsigned>(ctas), WARPS * 32, smem, s>>>(q);
     return cudaGetLastError();
