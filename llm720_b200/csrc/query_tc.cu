@@ -103,7 +103,7 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 const int m_blk = static_cast<int>(tile / H), h = static_cast<int>(tile % H);
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(empty_bar(stage), phase ^ 1, status)) { ok = false; break; }
+                    if (!mbar_wait_hint(empty_bar(stage), phase ^ 1, status)) { ok = false; break; }
                     mbar_expect_tx(full_bar(stage), stage_bytes);
                     tc::tma_load_2d(sA + stage * A_BYTES, &map_x, kb * BK, m_blk * BM, full_bar(stage));
                     tc::tma_load_2d(sB + stage * B_BYTES, &map_w, kb * BK, h * Q, full_bar(stage));
@@ -116,11 +116,11 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         if (lane == 0) {
             int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0; bool ok = true;
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-                if (!mbar_wait(acce_bar(acc), acc_phase ^ 1, status)) { ok = false; break; }
+                if (!mbar_wait_hint(acce_bar(acc), acc_phase ^ 1, status)) { ok = false; break; }
                 tc::fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * MAXQ;
                 for (int kb = 0; kb < num_kb; ++kb) {
-                    if (!mbar_wait(full_bar(stage), phase, status)) { ok = false; break; }
+                    if (!mbar_wait_hint(full_bar(stage), phase, status)) { ok = false; break; }
                     tc::fence_after_sync();
                     const uint64_t ad = tc::smem_desc_sw128(sA + stage * A_BYTES);
                     const uint64_t bd = tc::smem_desc_sw128(sB + stage * B_BYTES);
@@ -151,7 +151,7 @@ query_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const int m_blk = static_cast<int>(tile / H), h = static_cast<int>(tile % H);
             float* sb = s_bias + acc * MAXQ;
             for (int c = et; c < Q; c += EPI_THREADS) sb[c] = bias ? __bfloat162float(bias[h * Q + c]) : 0.f;
-            if (ok && !mbar_wait(accf_bar(acc), acc_phase, status)) ok = false;
+            if (ok && !mbar_wait_hint(accf_bar(acc), acc_phase, status)) ok = false;
             {   // one barrier publishes the bias and makes the decision the same in every epilogue thread
                 int all_ok;
                 asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.s32 q, %1, 0;\n\tbar.red.and.pred p, 1, 256, q;\n\t"

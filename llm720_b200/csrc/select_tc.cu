@@ -293,7 +293,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             uint32_t q_phase = 0; int stage = 0; uint32_t k_phase = 0; bool ok = true;
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (int hf = 0; hf < 2 && ok; ++hf) {
-                    if (!mbar_wait(q_empty, q_phase ^ 1, p.status)) { ok = false; break; }
+                    if (!mbar_wait_hint(q_empty, q_phase ^ 1, p.status)) { ok = false; break; }
                     q_phase ^= 1;
                     mbar_expect_tx(q_full, q_bytes);
                     for (int t = 0; t < 3; ++t)
@@ -304,7 +304,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     const CUtensorMap* mk = hf ? &map_k1 : &map_k0;
                     for (int c2 = 0; c2 < 2 * nch; ++c2) {          // two passes over the sub-keys
                         const int c = c2 < nch ? c2 : c2 - nch;
-                        if (!mbar_wait(k_empty(stage), k_phase ^ 1, p.status)) { ok = false; break; }
+                        if (!mbar_wait_hint(k_empty(stage), k_phase ^ 1, p.status)) { ok = false; break; }
                         mbar_expect_tx(k_full(stage), k_bytes);
                         for (int ka = 0; ka < KA; ++ka)
                             tc::tma_load_2d(sK + stage * K_STAGE_BYTES + ka * BOX_BYTES, mk, ka * 64, c * NC, k_full(stage));
@@ -320,13 +320,13 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
             uint32_t q_phase = 0; int stage = 0; uint32_t k_phase = 0; uint32_t g = 0; bool ok = true;
             for (int64_t tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
                 for (int hf = 0; hf < 2 && ok; ++hf) {
-                    if (!mbar_wait(q_full, q_phase, p.status)) { ok = false; break; }
+                    if (!mbar_wait_hint(q_full, q_phase, p.status)) { ok = false; break; }
                     q_phase ^= 1;
                     const int nch = hf ? nch1 : nch0;
                     for (int c = 0; c < 2 * nch; ++c, ++g) {
                         const int acc = g & (N_ACC - 1);
-                        if (!mbar_wait(acc_empty(acc), ((g / N_ACC) & 1) ^ 1, p.status)) { ok = false; break; }
-                        if (!mbar_wait(k_full(stage), k_phase, p.status)) { ok = false; break; }
+                        if (!mbar_wait_hint(acc_empty(acc), ((g / N_ACC) & 1) ^ 1, p.status)) { ok = false; break; }
+                        if (!mbar_wait_hint(k_full(stage), k_phase, p.status)) { ok = false; break; }
                         tc::fence_after_sync();
                         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * BM;
                         uint32_t first = 0;
@@ -377,7 +377,7 @@ select_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constan
                     for (int j = 0; j < 32; ++j) bnd[j] = pass ? s_tau[cg * 32 + j] : -INFINITY;
                     for (int ch = 0; ch < nch; ++ch, ++g) {
                         const int acc = g & (N_ACC - 1);
-                        if (ok && !mbar_wait(acc_full(acc), (g / N_ACC) & 1, p.status)) ok = false;
+                        if (ok && !mbar_wait_hint(acc_full(acc), (g / N_ACC) & 1, p.status)) ok = false;
                         if (!ok) continue;
                         tc::fence_after_sync();
                         uint32_t r[32];
