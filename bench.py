@@ -618,6 +618,10 @@ def run_c4(env, steps):
                                           "partial sums added in rank order"}
     if direct is not None and direct._xchg is not None:
         direct.close()
+    de = out["direct_exchange"]
+    faster = "ms_per_step" in de and de.get("agrees") and de["ms_per_step"] < out["ms_per_step"]
+    out["fastest_exchange"] = {"exchange": "direct" if faster else "collectives",
+                               "ms_per_step": de["ms_per_step"] if faster else out["ms_per_step"]}
     del layer, down, up
     torch.cuda.empty_cache()
     return out
