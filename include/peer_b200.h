@@ -342,6 +342,14 @@ int peer_usage_histogram(const int64_t* ids, int64_t n_ids, int64_t* counts, int
  * is recorded there and the offending access is skipped. */
 int peer_query_status(peer_handle_t h, void* stream);
 
+/* Inference with fixed weights: while `frozen` is set the caller promises that the sub-key tables it passes to this
+ * handle do not change, and what the selection derives from them (1/||key||, the normalised copy, the first pass's
+ * error bounds: one small launch per call otherwise) is computed by the first call and reused by every later call
+ * that brings the same two key pointers on the same stream.  Other pointers, another stream, or setting the flag
+ * again compute them anew.  Off by default: the reference's module reads its keys afresh in every forward
+ * (llm/models/experts.py:153-163), which is what training needs.  Only for two-dimensional key grids. */
+int peer_freeze_keys(peer_handle_t h, int frozen);
+
 /* Per-stage device timing, for benchmarks: while enabled, every slice of
  * peer_forward / peer_forward_host records CUDA events on its stream around
  * the three stage launches (query, select, expert evaluation).  Enabling or

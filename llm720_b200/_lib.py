@@ -82,6 +82,7 @@ EXPORTS = {
     "peer_usage_histogram": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
     "peer_query_status": (C.c_int, [C.c_void_p, C.c_void_p]),
     "peer_launch_count": (C.c_int64, [C.c_void_p]),
+    "peer_freeze_keys": (C.c_int, [C.c_void_p, C.c_int]),
     "peer_stage_timing": (C.c_int, [C.c_void_p, C.c_int]),
     "peer_stage_times": (C.c_int, [C.c_void_p, C.POINTER(C.c_double), C.POINTER(C.c_int64)]),
 }

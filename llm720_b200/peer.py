@@ -378,6 +378,11 @@ class PeerOp:
         with torch.cuda.device(self.device):
             self._check(self.lib.peer_query_status(self.handle, _stream(self.device)))
 
+    def freeze_keys(self, frozen: bool = True):
+        """Inference with fixed sub-keys: the per-call preparation of the key tables (norms, normalised copy, error
+        bounds) is done once and reused while the same key tensors come on the same stream (`peer_freeze_keys`)."""
+        self._check(self.lib.peer_freeze_keys(self.handle, int(frozen)))
+
     def stage_timing(self, enable: bool):
         """Record CUDA events around the three stage launches of every following forward."""
         self._check(self.lib.peer_stage_timing(self.handle, int(enable)))

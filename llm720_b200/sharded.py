@@ -204,10 +204,13 @@ class ShardedPEER:
     (`expert_down.weight` / `expert_up.weight` of shape [num_experts/world, D]);
     `num_experts` and `product_key_dim` describe the FULL table."""
 
-    def __init__(self, layer, group=None, exchange: str = "nccl"):
+    def __init__(self, layer, group=None, exchange: str = "nccl", freeze_keys: bool = True):
         if exchange not in ("nccl", "direct"):
             raise ValueError("exchange is 'nccl' (three collectives) or 'direct' (stores into the peers' memory)")
         self.layer, self.group, self.exchange = layer, group, exchange
+        # the layer is evaluated, never trained, here: the sub-keys' derived tables are prepared once per plan
+        # (pass freeze_keys=False if the sub-keys are updated in place between steps)
+        self.freeze_keys = freeze_keys
         self._buf, self._buf_key, self.last_counts = None, None, None
         self._xchg = None                 # direct exchange: the library's handle of this rank's region
         self.world = dist.get_world_size(group)
@@ -347,6 +350,7 @@ class ShardedPEER:
         bounds a decode-shaped batch)."""
         L, world, rank = self.layer, self.world, dist.get_rank(self.group)
         HK = L.num_heads * L.num_experts_per_tok
+        op.freeze_keys(self.freeze_keys)
         x_all = torch.empty(world * T, D, dtype=dtype, device=dev)
         send = torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev)
         recv = torch.empty(world, block_words(T, HK), dtype=torch.int32, device=dev)

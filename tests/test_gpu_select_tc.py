@@ -192,3 +192,30 @@ def test_stage_entry_equals_whole_layer_selection(cuda_device):
     rows, exact, near, bad = orc.compare_selection(ids2.cpu(), ids.cpu(), sc.cpu(), sc2.cpu())
     assert bad == 0 and exact >= 0.99 * rows, (rows, exact, near, bad)
     assert torch.allclose(sc, sc2, rtol=0, atol=2e-6)
+
+
+def test_frozen_keys_are_prepared_once_and_anew_for_other_tables(cuda_device):
+    """peer_freeze_keys: the key tables' derived data is reused for the same two tensors, recomputed for other
+    tensors and after the flag is set again; results equal those of a handle that prepares them in every call."""
+    T, H, Q, n, k = 48, 4, 256, (512, 384), 16
+    keys = [_keys(n[0], Q // 2, 71).to(cuda_device), _keys(n[1], Q // 2, 72).to(cuda_device)]
+    other = _keys(n[0], Q // 2, 73).to(cuda_device)
+    q = _queries(T, H, Q, 74).to(cuda_device).contiguous()
+    cfg = syn.PeerConfig("frozen", 64, 64, H, Q, n, k, torch.bfloat16, torch.bfloat16, 1, T)
+    plain, frozen = make_op(cfg, cuda_device, "product"), make_op(cfg, cuda_device, "product")
+    frozen.freeze_keys(True)
+    want = plain.select(q, keys[0], keys[1])
+    for _ in range(3):                                   # the first call prepares, the others reuse
+        got = frozen.select(q, keys[0], keys[1])
+        assert torch.equal(got[0], want[0]) and torch.equal(got[1], want[1])
+    want_other = plain.select(q, other, keys[1])
+    got = frozen.select(q, other, keys[1])               # another tensor: prepared anew
+    assert torch.equal(got[0], want_other[0]) and torch.equal(got[1], want_other[1])
+    assert not torch.equal(want_other[0], want[0])
+    keys[0].copy_(other)                                 # in place: the caller's promise is broken ...
+    frozen.select(q, keys[0], keys[1])
+    frozen.freeze_keys(True)                             # ... and renewed: prepared anew
+    got = frozen.select(q, keys[0], keys[1])
+    assert torch.equal(got[0], want_other[0]) and torch.equal(got[1], want_other[1])
+    frozen.query_status()
+
